@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the realized-kernel hot path on B200.
+
+Workload (config "fused elementwise+reduce chain f32"): a, b, c [8192,8192] ~
+N(0,1) from seed; one step = the forward kernel y = sum_last(relu(a*b+c)) plus
+its VJP kernel g = b * (a*b+c > 0), the two dispatches the reference's scheduler
+emits for that config, issued through the C ABI of libthvm_cuda.so
+(thvm_cuda_dispatch_kernel_rs).  Metric: algorithmic HBM bytes per second,
+    forward  3*8192^2*4 + 8192*4 =   805,339,136 B
+    backward 4*8192^2*4          = 1,073,741,824 B   per step 1,879,080,960 B.
+The three inputs (805 MB) are larger than the 126 MB L2, so every step streams
+from HBM.
+
+`value`  inputs resident in HBM, CUDA events on the library's stream.
+`e2e`    the same step with HOST buffers: buf_write of a, b, c from pinned memory,
+         both dispatches, buf_read of y and g, wall clock.
+`--impl reference` times the reference's own CPU backend (oracle/_ref, built from
+the reference's sources; else the CPU restatement in oracle/) on a bounded row
+sample of the same workload.
+
+The path does not shard: with --gpus N every rank runs an independent replica
+("scaling": "weak"), no collective on the data path.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS, COLS = 8192, 8192
+FWD_BYTES = 3 * ROWS * COLS * 4 + ROWS * 4
+BWD_BYTES = 4 * ROWS * COLS * 4
+METRIC, UNIT = "fused_kernel_hbm_gbs", "GB/s"
+WORKLOAD = "cfg2 fused chain f32: y=sum_last(relu(a*b+c)) + VJP wrt a, a,b,c [8192,8192]"
+
+
+def chain_dispatches(rows: int, cols: int, arrays):
+    """The two dispatches of the config, as the reference's fuser emits them."""
+    from tinyhvm_b200 import abi
+    from tinyhvm_b200.abi import ADD, CMP, MUL, RELU, SUM, Dispatch, Leaf
+    v = abi.view_contiguous([rows, cols])
+    a, b, c = (Leaf(x, v) for x in arrays)
+    zero = Leaf(np.zeros(1, dtype=np.float32), abi.view_contiguous([1, 1]))
+    fwd = Dispatch([a, b, c], [(MUL, 0, 1), (ADD, 3, 2), (RELU, 4, 0)], [rows, cols], [1], SUM, name="chain_fwd")
+    bwd = Dispatch([a, b, c, zero], [(MUL, 0, 1), (ADD, 4, 2), (CMP, 5, 3), (MUL, 1, 6)], [rows, cols], name="chain_bwd")
+    return fwd, bwd
+
+
+def make_inputs(rows: int, cols: int, rank: int):
+    from tinyhvm_b200 import synth
+    seed = synth.SEED_BASE + 2 + 1000 * rank
+    return [synth.normal(seed, t, rows * cols) for t in range(3)]
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for ts, r in self.rows if t0 - 0.05 <= ts <= t1 + 0.15] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_run(rows: int, arrays, repeat: int = 1):
+    """Forward + backward on the CPU checker over `rows` rows; returns (seconds, kind)."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import checkers
+    impl = checkers.Reference.try_load()
+    kind = "reference"
+    if impl is None:
+        impl, kind = checkers.Oracle(), "port"
+    sub = [x[: rows * COLS] for x in arrays]
+    fwd, bwd = chain_dispatches(rows, COLS, sub)
+    best = float("inf")
+    for _ in range(repeat):
+        t = time.perf_counter()
+        impl.run(fwd); impl.run(bwd)
+        best = min(best, time.perf_counter() - t)
+    return best, kind
+
+
+def reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    rows = 1024                                  # 1/8 of the workload per step: seconds, not minutes
+    arrays = make_inputs(rows, COLS, 0)
+    for _ in range(min(args.warmup, 1)):
+        cpu_run(rows, arrays)
+    times = [cpu_run(rows, arrays)[0] for _ in range(min(args.steps, 5))]
+    _, kind = cpu_run(16, arrays)
+    sec = statistics.mean(times)
+    nbytes = (FWD_BYTES + BWD_BYTES) * rows / ROWS
+    val = nbytes / sec / 1e9
+    sample = f"{rows} of {ROWS} rows per step (fwd+bwd), {len(times)} steps, single-threaded scalar interpreter"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3 * ROWS / rows, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import tinyhvm_b200
+    from tinyhvm_b200 import abi
+
+    os.environ.setdefault("THVM_CUDA_DEVICE", str(local))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    be = tinyhvm_b200.CudaBackend()
+    lib = be.lib
+    stream = torch.cuda.ExternalStream(lib.thvm_cuda_stream(), device=torch.device("cuda", local))
+    rows = args.rows
+    scale = rows / ROWS
+    fwd_bytes, bwd_bytes = 3 * rows * COLS * 4 + rows * 4, 4 * rows * COLS * 4
+
+    # inputs: generated on the host, pinned, uploaded once for the resident runs
+    host = [torch.from_numpy(x).pin_memory() for x in make_inputs(rows, COLS, rank)]
+    arrays = [h.numpy() for h in host]
+    fwd, bwd = chain_dispatches(rows, COLS, arrays)
+    ids = [be.alloc(a.nbytes) for a in arrays]
+    for i, a in zip(ids, arrays):
+        lib.thvm_cuda_buf_write(i, a.ctypes.data, a.nbytes)
+    zero_id = be.upload(np.zeros(1, dtype=np.float32))
+    y_id, g_id = be.alloc(rows * 4), be.alloc(rows * COLS * 4)
+    y_host = torch.empty(rows, dtype=torch.float32).pin_memory()
+    g_host = torch.empty(rows * COLS, dtype=torch.float32).pin_memory()
+
+    def step():
+        be.dispatch_ids(y_id, ids, fwd)
+        be.dispatch_ids(g_id, ids + [zero_id], bwd)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        be.sync()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    plan_fwd = plan_bwd = ""
+    be.dispatch_ids(y_id, ids, fwd); plan_fwd = be.last_plan()
+    be.dispatch_ids(g_id, ids + [zero_id], bwd); plan_bwd = be.last_plan()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream
+    sampler = ClockSampler(local)
+    time.sleep(0.3)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = be.launches()
+    barrier()
+    t0 = time.time()
+    for k in range(args.steps):
+        ev[k][0].record(stream)
+        be.dispatch_ids(y_id, ids, fwd)
+        ev[k][1].record(stream)
+        be.dispatch_ids(g_id, ids + [zero_id], bwd)
+        ev[k][2].record(stream)
+    barrier()
+    t1 = time.time()
+    launches = be.launches() - launches0
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    clocks = sampler.stop(t0, t1)
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end with host buffers through the same C ABI
+    e2e_steps = max(3, min(args.steps, 5))
+
+    def e2e_step():
+        for i, a in zip(ids, arrays):
+            lib.thvm_cuda_buf_write(i, a.ctypes.data, a.nbytes)
+        step()
+        lib.thvm_cuda_buf_read_nosync(g_id, g_host.data_ptr(), g_host.numel() * 4)
+        lib.thvm_cuda_buf_read(y_id, y_host.data_ptr(), y_host.numel() * 4)
+
+    e2e_step()
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = world * (fwd_bytes + bwd_bytes) / (e2e_ms * 1e-3) / 1e9
+
+    # ---- checks on the result of the timed runs (size-independent properties)
+    y = y_host.numpy()
+    g = g_host.numpy()
+    a, b, c = arrays
+    probe = slice(0, 4 * COLS)
+    u = a[probe] * b[probe] + c[probe]
+    ok_g = np.array_equal(g[probe], np.where(u > 0, b[probe], np.float32(0)) * np.float32(1.0) + np.float32(0))
+    y_ref = np.maximum(u, 0).reshape(4, COLS).astype(np.float64).sum(axis=1)
+    ok_y = np.allclose(y[:4], y_ref, rtol=1e-5)
+    err = be.last_error()
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        dom = ("chain_bwd", plan_bwd, bwd_bytes, bwd_ms) if bwd_ms >= fwd_ms else ("chain_fwd", plan_fwd, fwd_bytes, fwd_ms)
+        oth = ("chain_fwd", plan_fwd, fwd_bytes, fwd_ms) if bwd_ms >= fwd_ms else ("chain_bwd", plan_bwd, bwd_bytes, bwd_ms)
+
+        def roof(t):
+            ach = t[2] / (t[3] * 1e-3) / 1e9
+            return {"kernel": f"{t[0]} ({t[1]})", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                    "frac": ach / peak, "traffic": None, "ms_per_launch": t[3], "algorithmic_bytes": t[2], "peak_source": peak_src}
+
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD if rows == ROWS else f"{WORKLOAD} (rows={rows})",
+                                            "l2": "inputs (805 MB) larger than L2; no flush needed", "parallelism": f"replicas x{world}"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(sum(x.nbytes for x in arrays)),
+                    "d2h_bytes_per_step": int(g_host.numel() * 4 + y_host.numel() * 4), "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": roof(dom), "roofline_other": roof(oth),
+            "checks": {"y_rows0_3_vs_f64": bool(ok_y), "g_rows0_3_bit_exact": bool(ok_g), "backend_error": err},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            sample_rows = 512
+            sec, kind = cpu_run(sample_rows, [x[: sample_rows * COLS] for x in arrays], repeat=2)
+            line["cpu_baseline"] = {"value": (FWD_BYTES + BWD_BYTES) * (sample_rows / ROWS) / sec / 1e9, "unit": UNIT,
+                                    "cores": 1, "kind": kind,
+                                    "sample": f"{sample_rows} of {ROWS} rows, fwd+bwd, best of 2 ({sec:.2f} s)"}
+        print(json.dumps(line))
+    be.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

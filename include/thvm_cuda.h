@@ -1,0 +1,227 @@
+/* thvm_cuda.h — C ABI of libthvm_cuda.so, the B200 (sm_100a) backend for
+ * TinyHVM's realized-kernel path.
+ *
+ * Every entry point below has exactly the signature of one slot of the
+ * reference's `struct Backend` vtable (reference: src/tinyhvm.h:988-1046), so
+ * a `Backend cuda_backend = { .init = thvm_cuda_init, ... }` is a drop-in
+ * beside `cpu_backend` (reference: src/backend/cpu/_.c:21-35).  The POD
+ * structs are layout-identical mirrors of the reference's `Shape`, `View`,
+ * `ShapeTracker`, `FusedOp`, `ReduceSpec`, `KOp` and `UOpKernel`
+ * (reference: src/tinyhvm.h:531-717); the vtable shim static_asserts the
+ * sizes against the reference header.
+ *
+ * State is process-global (the vtable has no context argument): one process
+ * drives one GPU.  All work is issued on one CUDA stream; `buf_read`
+ * synchronises it.  Nothing here falls back to the CPU: without a CUDA device
+ * `thvm_cuda_init` returns non-zero and every other call aborts.
+ */
+#ifndef THVM_CUDA_H
+#define THVM_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- limits (reference: src/tinyhvm.h:528-529, 571, 657-658, 674, 720) ---- */
+#define THC_MAX_DIM      8
+#define THC_MAX_VIEWS    4
+#define THC_MAX_OPS      64
+#define THC_MAX_LEAVES   64
+#define THC_KOP_MAX      512
+#define THC_MAX_BUFS     16384
+
+/* ---- dtypes (reference: src/tinyhvm.h:417-421) ---- */
+#define THC_F32 0
+#define THC_F16 1
+#define THC_I32 2
+#define THC_U32 3
+
+/* ---- UOp codes that reach the backend (reference: src/tinyhvm.h:116-137) ---- */
+#define THC_NEG   3
+#define THC_EXP   4
+#define THC_LOG   5
+#define THC_RELU  6
+#define THC_CAST  7
+#define THC_SQRT  8
+#define THC_ADD   9
+#define THC_MUL  10
+#define THC_DIV  11
+#define THC_MAX  12
+#define THC_CMP  13
+#define THC_SUB  14
+#define THC_SUM  15
+#define THC_RMAX 16
+
+/* ---- POD mirrors ---- */
+typedef struct {                       /* Shape, src/tinyhvm.h:531-534 */
+    uint32_t dims[THC_MAX_DIM];
+    uint32_t rank;
+} thc_shape_t;
+
+typedef struct {                       /* View, src/tinyhvm.h:549-566 */
+    thc_shape_t shape;
+    int32_t  strides[THC_MAX_DIM];     /* elements; 0 = broadcast */
+    int32_t  offset;                   /* elements; may be negative (PAD) */
+    uint32_t numel;
+    uint8_t  contiguous;
+    uint8_t  has_mask;
+    uint32_t mask_begin[THC_MAX_DIM];
+    uint32_t mask_end[THC_MAX_DIM];
+    uint8_t  n_compound_masks;
+    struct { uint8_t dim_a, dim_b; int32_t stride_a; uint32_t begin, end; } compound_masks[2];
+    uint32_t mod_size[THC_MAX_DIM];
+} thc_view_t;
+
+typedef struct {                       /* ShapeTracker, src/tinyhvm.h:571-575 */
+    thc_view_t views[THC_MAX_VIEWS];
+    uint8_t    n_views;
+} thc_tracker_t;
+
+typedef struct {                       /* FusedOp, src/tinyhvm.h:659 */
+    uint32_t uop, arg_a, arg_b, aux;
+} thc_fused_op_t;
+
+typedef struct {                       /* ReduceSpec, src/tinyhvm.h:660-672 */
+    uint8_t  is_reduce[THC_MAX_DIM];
+    uint32_t reduce_type;              /* 0, THC_SUM or THC_RMAX */
+    uint32_t post_reduce_start;
+    uint32_t n_post_leaves;
+    uint32_t reduce2_type;
+    uint32_t reduce2_start;
+    uint8_t  is_reduce2[THC_MAX_DIM];
+} thc_reduce_spec_t;
+
+typedef enum {                         /* KOpType, src/tinyhvm.h:675-691 */
+    THC_KOP_NOOP = 0, THC_KOP_GID, THC_KOP_CONST_F, THC_KOP_CONST_U,
+    THC_KOP_RANGE, THC_KOP_ENDRANGE, THC_KOP_LOAD, THC_KOP_STORE,
+    THC_KOP_ALU, THC_KOP_ACC_INIT, THC_KOP_ACC, THC_KOP_IDX,
+    THC_KOP_MOD, THC_KOP_DIV, THC_KOP_MASK
+} thc_kop_type_t;
+
+typedef struct {                       /* KOp, src/tinyhvm.h:693-700 */
+    thc_kop_type_t type;
+    uint32_t arg[3];
+    union { float f; uint32_t u; } imm;
+} thc_kop_t;
+
+typedef struct {                       /* UOpKernel, src/tinyhvm.h:702-717 */
+    thc_kop_t   ops[THC_KOP_MAX];
+    uint32_t    n_ops, n_bufs, n_leaves;
+    thc_view_t  leaf_views[THC_MAX_LEAVES];
+    uint32_t    leaf_dtypes[THC_MAX_LEAVES];
+    uint32_t    coord_uop[THC_MAX_DIM];
+    uint32_t    rank;
+    thc_shape_t full_shape;
+    uint32_t    grid[3], tg[3];
+    uint32_t    local_size, reduce_numel, out_dtype;
+} thc_uop_kernel_t;
+
+/* ================= vtable entry points (one per Backend slot) ================= */
+
+/* Backend.init / shutdown — src/tinyhvm.h:990-991 (CPU: src/backend/cpu/pool.c:12-13).
+ * Device = $THVM_CUDA_DEVICE, else $LOCAL_RANK, else 0.  Returns 0 on success. */
+int      thvm_cuda_init(void);
+void     thvm_cuda_shutdown(void);
+
+/* Buffers — src/tinyhvm.h:994-1001 (CPU: src/backend/cpu/pool.c:14-17).
+ * Ids are small integers handed out in increasing order, 0 = failure.  Fresh
+ * buffers read as zero.  `decref` frees at refcount 0 unless id <= the
+ * persistent floor. */
+uint32_t thvm_cuda_buf_alloc(uint64_t bytes);
+void     thvm_cuda_buf_free(uint32_t id);
+void     thvm_cuda_buf_incref(uint32_t id);
+void     thvm_cuda_buf_decref(uint32_t id);
+void     thvm_cuda_mem_checkpoint(uint32_t *leaf_buf_ids, uint32_t n_leaves);
+void     thvm_cuda_buf_mark_use(uint32_t id);
+void     thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes);
+void     thvm_cuda_buf_read(uint32_t id, void *out, uint64_t bytes);
+
+/* Single-op forms — src/tinyhvm.h:1004-1016 (CPU: src/backend/cpu/ops.c:15-130). */
+void     thvm_cuda_op_unary(uint32_t uop, uint32_t dst, const thc_view_t *dv, uint32_t dst_dtype,
+                            uint32_t src, const thc_view_t *sv, uint32_t src_dtype);
+void     thvm_cuda_op_binary(uint32_t uop, uint32_t dst, const thc_view_t *dv, uint32_t dst_dtype,
+                             uint32_t a, const thc_view_t *av, uint32_t a_dtype,
+                             uint32_t b, const thc_view_t *bv, uint32_t b_dtype);
+void     thvm_cuda_op_mm(uint32_t dst, uint32_t dst_dtype,
+                         uint32_t a, const thc_view_t *av, uint32_t a_dtype,
+                         uint32_t b, const thc_view_t *bv, uint32_t b_dtype,
+                         uint32_t M, uint32_t K, uint32_t N);
+void     thvm_cuda_op_reduce(uint32_t uop, uint32_t dst, uint32_t dst_numel, uint32_t dst_dtype,
+                             uint32_t src, uint32_t src_numel, uint32_t src_dtype, uint32_t reduce_dim);
+
+/* Fused elementwise(+reduce) kernel over strided/broadcast/masked views —
+ * src/tinyhvm.h:1019-1025 (CPU: src/backend/cpu/dispatch.c:119-282; caller:
+ * src/schedule/_.c:2370-2378).  `leaf_sts` may be NULL; `reduce` may be NULL;
+ * side outputs are ignored as in the CPU backend. */
+void     thvm_cuda_dispatch_kernel_rs(uint32_t out_buf,
+                                      uint32_t *leaf_bufs, const thc_view_t **leaf_views,
+                                      const thc_tracker_t *const *leaf_sts, uint32_t n_leaves,
+                                      thc_fused_op_t *ops, uint32_t n_ops,
+                                      const thc_shape_t *full_shape, const thc_reduce_spec_t *reduce,
+                                      uint32_t *side_bufs, const uint32_t *side_op_indices,
+                                      uint32_t n_side_outputs,
+                                      const uint32_t *leaf_dtypes, uint32_t out_dtype);
+
+/* Lowered KOP program — src/tinyhvm.h:1026-1028 (CPU: src/backend/cpu/uop.c:118-155).
+ * Every KOP_LOAD is bounds-checked against the pool's recorded buffer size. */
+void     thvm_cuda_dispatch_uop_kernel(uint32_t out_buf, const uint32_t *leaf_bufs, uint32_t n_leaves,
+                                       const thc_uop_kernel_t *kernel, uint64_t cache_key);
+
+/* Strided view -> contiguous f32 copy, device-to-device copy, unsynchronised
+ * read — src/tinyhvm.h:1029-1031 (callers: src/interact/tensor_ops.c:93-147). */
+void     thvm_cuda_contiguify(uint32_t dst_buf, uint32_t numel, uint32_t src_buf, const thc_view_t *src_view);
+void     thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes);
+void     thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes);
+
+/* In-place Adam — src/tinyhvm.h:1033-1035 (math: src/shaders.metal:406-420). */
+void     thvm_cuda_adam_step(uint32_t param, uint32_t grad, uint32_t m, uint32_t v,
+                             float lr, float beta1, float beta2, float eps,
+                             float bc1, float bc2, uint32_t n);
+
+/* Pool — src/tinyhvm.h:1038-1039 (CPU: src/backend/cpu/pool.c:19-26).
+ * `pool_reset(keep)` frees ids > keep and rewinds the id counter to keep+1. */
+void     thvm_cuda_pool_reset(uint32_t keep);
+void     thvm_cuda_pool_set_persistent(uint32_t max_buf);
+
+/* Batching / profiling — src/tinyhvm.h:1041-1045. */
+void     thvm_cuda_begin_batch(void);
+void     thvm_cuda_end_batch(void);
+void     thvm_cuda_profile_report(void);
+void     thvm_cuda_profile_reset(void);
+
+/* ================= additions with no vtable slot ================= */
+
+/* Sticky last-error text ("" when none).  The vtable returns void almost
+ * everywhere (the reference exits on error); a host can poll this instead. */
+const char *thvm_cuda_last_error(void);
+void        thvm_cuda_clear_error(void);
+
+/* The backend's CUDA stream (a cudaStream_t) and a blocking wait on it, so a
+ * host can time with CUDA events on the launching stream. */
+void    *thvm_cuda_stream(void);
+void     thvm_cuda_sync(void);
+/* Raw device pointer / byte size of a live buffer (NULL / 0 if not live). */
+void    *thvm_cuda_buf_ptr(uint32_t id);
+uint64_t thvm_cuda_buf_bytes(uint32_t id);
+/* Kernel launches issued by this library since init (or the last reset). */
+uint64_t thvm_cuda_launch_count(void);
+/* Name of the kernel family chosen for the most recent dispatch ("ew_vec4",
+ * "reduce_inner", "generic", ...), for tests and profiles. */
+const char *thvm_cuda_last_plan(void);
+/* Plan selection override for tests: 0 = automatic, 1 = always the generic
+ * descriptor-driven kernel. */
+void     thvm_cuda_set_force_generic(int on);
+
+/* Signature of a dispatch, the same FNV-style mix the reference computes as
+ * `normalized_sig` (src/tinyhvm.h:828-856); the plan cache is keyed by it. */
+uint64_t thvm_cuda_signature(const thc_fused_op_t *ops, uint32_t n_ops,
+                             const thc_view_t *const *leaf_views,
+                             const thc_tracker_t *const *leaf_sts, uint32_t n_leaves,
+                             const thc_shape_t *full_shape, const thc_reduce_spec_t *reduce);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THVM_CUDA_H */

@@ -1,0 +1,180 @@
+"""Parity of the CUDA path with the oracle, through the C ABI, on a B200.
+
+Tolerances (from the stated target): integer / index outputs bit-exact; f32
+elementwise bit-exact unless the chain holds EXP or LOG (device libm differs
+from glibc in the last ulp: 1e-5 relative); reductions 1e-5 relative, with an
+absolute floor of 1e-5 x the RMS of the output tensor for sums that cancel;
+MUL+SUM contractions (matmul / conv) 1e-4 on the same measure.
+"""
+import numpy as np
+import pytest
+
+import cases
+from test_oracle_pins import all_cases, dtype_cast_dispatches, golden_case_list, golden_dispatches, run_chain, same, GOLDEN
+from tinyhvm_b200 import abi
+from tinyhvm_b200.abi import EXP, F16, F32, I32, LOG, MUL, SUM, U32
+
+pytestmark = pytest.mark.gpu
+
+
+def as_float(arr, dtype):
+    if dtype == F16:
+        return arr.view(np.float16).astype(np.float64)
+    return arr.astype(np.float64)
+
+
+def is_contraction(d):
+    return d.reduce_type == SUM and len(d.ops) == 1 and d.ops[0][0] == MUL and len(d.leaves) == 2
+
+
+def check(d, got, want, strict_serial=False):
+    """Compare one dispatch's output with the oracle's under the stated tolerances."""
+    inexact_ops = any(o[0] in (EXP, LOG) for o in d.ops)
+    red_n = int(np.prod([d.full[a] for a in d.reduce_axes])) if d.reduce_type else 1
+    reordered = d.reduce_type == SUM and d.out_dtype == F32 and (red_n > 64 or not strict_serial)
+    if not inexact_ops and not reordered:
+        assert same(got, want), f"{d.name}: not bit-exact"
+        return
+    g, w = as_float(got, d.out_dtype), as_float(want, d.out_dtype)
+    finite = np.isfinite(w)
+    assert np.array_equal(np.isnan(g), np.isnan(w)) or d.out_dtype != F32 or inexact_ops, f"{d.name}: NaN pattern differs"
+    if d.out_dtype in (I32, U32):
+        assert np.max(np.abs(g - w)) <= 1 + 1e-5 * np.max(np.abs(w)), d.name    # a truncated value may sit on an integer boundary
+        return
+    rtol = 1e-4 if is_contraction(d) else 1e-5
+    if d.out_dtype == F16:
+        rtol = 1e-3                                                             # one half-precision ulp
+    rms = float(np.sqrt(np.mean(w[finite] ** 2))) if finite.any() else 0.0
+    err = np.abs(g[finite] - w[finite])
+    bound = rtol * np.abs(w[finite]) + rtol * rms + 1e-30
+    assert np.all(err <= bound), f"{d.name}: max excess {np.max(err / bound):.2f}x over rtol {rtol}"
+    assert np.array_equal(g[~finite], w[~finite], equal_nan=True) or inexact_ops, d.name
+
+
+@pytest.mark.parametrize("generic", [False, True], ids=["auto", "generic"])
+def test_named_and_fuzzed_dispatches(cuda, oracle, generic):
+    cuda.force_generic(generic)
+    try:
+        plans = {}
+        for d in all_cases():
+            got, want = cuda.run(d), oracle.run(d)
+            check(d, got, want, strict_serial=generic)
+            plans[cuda.last_plan()] = plans.get(cuda.last_plan(), 0) + 1
+        print("plans used:", plans)
+        assert cuda.last_error() == ""
+    finally:
+        cuda.force_generic(False)
+
+
+def test_reference_golden_vectors_on_gpu(cuda):
+    for name, chain, want, tol in golden_dispatches():
+        got = run_chain(cuda, chain)
+        assert np.allclose(got, want, rtol=max(tol, 1e-6), atol=max(tol, 1e-6)), (name, got, want)
+    for name, d, want in dtype_cast_dispatches():
+        assert same(cuda.run(d), want), name
+
+
+def test_committed_fixtures_on_gpu(cuda):
+    z = np.load(GOLDEN / "boundary_cases.npz")
+    for key, d in golden_case_list():
+        check(d, cuda.run(d), z[key])
+
+
+def test_pool_contract(cuda):
+    """ids ascend from the floor, fresh buffers are zero, pool_reset rewinds the counter,
+    decref below the persistent floor is ignored (src/backend/cpu/pool.c:14-26)."""
+    lib = cuda.lib
+    a = cuda.alloc(64)
+    b = cuda.alloc(1 << 20)
+    assert b == a + 1
+    assert not cuda.read(b, np.uint8, 1 << 20).any()
+    x = np.arange(1 << 18, dtype=np.float32)
+    cuda.write(b, x)
+    assert np.array_equal(cuda.read(b, np.float32, 1 << 18), x)
+    big = np.arange(3 << 20, dtype=np.float32)            # > 1 MiB: direct (unstaged) path
+    c = cuda.upload(big)
+    assert np.array_equal(cuda.read(c, np.float32, big.size), big)
+    d = cuda.alloc(big.nbytes)
+    lib.thvm_cuda_buf_copy(d, c, big.nbytes)
+    assert np.array_equal(cuda.read(d, np.float32, big.size), big)
+    lib.thvm_cuda_pool_set_persistent(a)
+    lib.thvm_cuda_buf_decref(a)
+    assert lib.thvm_cuda_buf_bytes(a) == 64                # persistent: still live
+    lib.thvm_cuda_buf_incref(b); lib.thvm_cuda_buf_decref(b)
+    assert lib.thvm_cuda_buf_bytes(b) == 1 << 20
+    lib.thvm_cuda_buf_decref(b)
+    assert lib.thvm_cuda_buf_bytes(b) == 0                 # freed at refcount 0
+    lib.thvm_cuda_pool_set_persistent(0)
+    cuda.reset(a - 1)
+    assert cuda.alloc(16) == a                             # counter rewound
+    cuda.reset(a - 1)
+    # reads past the end of a buffer return zeros
+    e = cuda.upload(np.ones(4, dtype=np.float32))
+    assert cuda.read(e, np.float32, 8).tolist() == [1, 1, 1, 1, 0, 0, 0, 0]
+    cuda.reset(e - 1)
+
+
+def test_out_of_range_load_is_caught_not_faulted(cuda):
+    """A view that addresses past its buffer reads 0 and raises the status word
+    (the CPU backend would read out of bounds)."""
+    v = abi.view_contiguous([8])
+    d = abi.Dispatch([abi.Leaf(np.ones(4, dtype=np.float32), v)], [], [8])
+    got = cuda.run(d)
+    assert got.tolist() == [1, 1, 1, 1, 0, 0, 0, 0]
+    assert "out of bounds" in cuda.last_error()
+    cuda.clear_error()
+
+
+def test_single_op_forms(cuda, oracle):
+    """op_unary / op_binary / op_mm / op_reduce / contiguify / adam_step against the oracle."""
+    import ctypes as C
+    lib, ol = cuda.lib, oracle.lib
+    rng = np.random.default_rng(5)
+    vp = C.c_void_p
+    x = rng.standard_normal(6 * 7).astype(np.float32)
+    y = rng.standard_normal(6 * 7).astype(np.float32)
+    dv = abi.view_contiguous([6, 7])
+    tv = abi.view_permute(abi.view_contiguous([7, 6]), [1, 0])
+    first = cuda.alloc(16)
+    bx, by, bo = cuda.upload(x), cuda.upload(y), cuda.alloc(x.nbytes)
+    for uop in (abi.NEG, abi.RELU, abi.SQRT, abi.EXP):
+        lib.thvm_cuda_op_unary(uop, bo, C.byref(dv), F32, bx, C.byref(tv), F32)
+        want = np.zeros_like(x)
+        ol.oracle_op_unary(C.c_uint32(uop), vp(want.ctypes.data), C.byref(dv), C.c_uint32(F32), vp(x.ctypes.data), C.byref(tv), C.c_uint32(F32))
+        got = cuda.read(bo, np.float32, x.size)
+        assert np.allclose(got, want, rtol=1e-5, atol=0, equal_nan=True), uop
+    for uop in (abi.ADD, abi.MUL, abi.DIV, abi.SUB, abi.MAX, abi.CMP):
+        lib.thvm_cuda_op_binary(uop, bo, C.byref(dv), F32, bx, C.byref(tv), F32, by, C.byref(dv), F32)
+        want = np.zeros_like(x)
+        ol.oracle_op_binary(C.c_uint32(uop), vp(want.ctypes.data), C.byref(dv), C.c_uint32(F32), vp(x.ctypes.data), C.byref(tv),
+                            C.c_uint32(F32), vp(y.ctypes.data), C.byref(dv), C.c_uint32(F32))
+        assert same(cuda.read(bo, np.float32, x.size), want), uop
+    # mm: [6,7] (transposed storage) @ [7,6]
+    bv = abi.view_contiguous([7, 6])
+    bm = cuda.alloc(36 * 4)
+    lib.thvm_cuda_op_mm(bm, F32, bx, C.byref(tv), F32, by, C.byref(bv), F32, 6, 7, 6)
+    want = np.zeros(36, dtype=np.float32)
+    ol.oracle_op_mm(vp(want.ctypes.data), C.c_uint32(F32), vp(x.ctypes.data), C.byref(tv), C.c_uint32(F32), vp(y.ctypes.data),
+                    C.byref(bv), C.c_uint32(F32), C.c_uint32(6), C.c_uint32(7), C.c_uint32(6))
+    assert np.allclose(cuda.read(bm, np.float32, 36), want, rtol=1e-5, atol=1e-6)
+    # reduce over the last dim
+    br = cuda.alloc(6 * 4)
+    for uop in (abi.SUM, abi.RMAX):
+        lib.thvm_cuda_op_reduce(uop, br, 6, F32, bx, 42, F32, 7)
+        want = np.zeros(6, dtype=np.float32)
+        ol.oracle_op_reduce(C.c_uint32(uop), vp(want.ctypes.data), C.c_uint32(6), C.c_uint32(F32), vp(x.ctypes.data), C.c_uint32(F32), C.c_uint32(7))
+        assert np.allclose(cuda.read(br, np.float32, 6), want, rtol=1e-6, atol=1e-6), uop
+    # contiguify a transposed view
+    lib.thvm_cuda_contiguify(bo, 42, bx, C.byref(tv))
+    assert np.array_equal(cuda.read(bo, np.float32, 42), x.reshape(7, 6).T.ravel())
+    # adam
+    n = 1000
+    p, g_, m, v = (rng.standard_normal(n).astype(np.float32) for _ in range(4))
+    v = np.abs(v)
+    ids = [cuda.upload(a) for a in (p, g_, m, v)]
+    lib.thvm_cuda_adam_step(*ids, 1e-3, 0.9, 0.999, 1e-8, 0.1, 0.001, n)
+    ol.oracle_adam_step(vp(p.ctypes.data), vp(g_.ctypes.data), vp(m.ctypes.data), vp(v.ctypes.data), C.c_float(1e-3), C.c_float(0.9),
+                        C.c_float(0.999), C.c_float(1e-8), C.c_float(0.1), C.c_float(0.001), C.c_uint32(n))
+    assert np.allclose(cuda.read(ids[0], np.float32, n), p, rtol=1e-6, atol=1e-7)
+    assert same(cuda.read(ids[2], np.float32, n), m) and same(cuda.read(ids[3], np.float32, n), v)
+    cuda.reset(first - 1)

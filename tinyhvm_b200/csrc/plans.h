@@ -1,0 +1,32 @@
+// plans.h — a cached plan for one dispatch signature: which kernel family
+// runs it and the family's precomputed parameters.
+#pragma once
+#include "gen_desc.h"
+
+namespace thc {
+
+enum PlanKind : int {
+    PLAN_GENERIC = 0,   // descriptor-driven interpreter (generic.cu)
+    PLAN_EW,            // collapsed-dims elementwise, vectorised inner dim (ew.cu)
+    PLAN_REDUCE,        // collapsed-dims reduce (reduce.cu)
+    PLAN_CONTRACT,      // SUM(MUL(a,b)) with separable operands -> GEMM (gemm.cu)
+};
+
+struct FastDesc;        // family-specific, defined in fast_desc.h
+
+struct Plan {
+    int        kind = PLAN_GENERIC;
+    GenDesc    host;                    // full description (host copy)
+    GenDesc   *dev_desc = nullptr;      // uploaded lazily, only if the generic kernel runs
+    DTracker  *dev_trackers = nullptr;
+    uint32_t   n_trackers = 0;
+    FastDesc  *fast = nullptr;          // owned; null for PLAN_GENERIC
+};
+
+// Decide the family for a freshly built plan (sets kind / fast).
+void classify_plan(Plan *p);
+// Launch a non-generic plan; false means "could not, use the generic kernel".
+bool launch_fast(Plan *p, const GenArgs &args);
+void free_fast(Plan *p);
+
+}  // namespace thc

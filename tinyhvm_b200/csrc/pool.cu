@@ -1,0 +1,335 @@
+// pool.cu — lifecycle, the device buffer pool behind the reference's integer
+// buffer ids, and host<->device transfers.
+//
+// Contract followed (reference: src/tinyhvm.h:990-1001,1030-1031,1038-1039):
+//   * ids are handed out in increasing order starting at 1; 0 means failure;
+//     pool_reset(keep) frees ids > keep and rewinds the counter to keep+1
+//     (src/backend/cpu/pool.c:14,19-26) — the scheduler indexes per-buffer
+//     epochs by id (src/schedule/_.c:55), so the numbering must match;
+//   * a fresh buffer reads as zero (the CPU backend callocs);
+//   * buf_write may return before the DMA ran only if the source was staged,
+//     because callers free the source right away (src/nn/loss.c:31-34);
+//   * buf_read returns finished data, so it drains the stream
+//     (src/ops/_.c:317-319 reads the result immediately);
+//   * decref frees at zero unless the id is at or below the persistent floor
+//     (Metal pool: src/backend/metal/pool.m:144-152).
+// Memory comes from the device's stream-ordered pool (cudaMallocAsync) with the
+// release threshold lifted, so a training step recycles its buffers without
+// going back to the driver.  Buffers of <= 256 bytes written by the host (the
+// reference turns every shape/axes/scalar constant into such a buffer) keep a
+// host shadow, so reading them back never waits for the GPU.
+#include <stdarg.h>
+#include <string.h>
+#include <map>
+#include "state.h"
+
+namespace thc {
+
+State g;
+
+static const uint64_t RING_BYTES   = 16ull << 20;   // two 8 MiB halves
+static const uint64_t RING_MAX_MSG = 1ull << 20;    // larger writes go direct
+static const uint64_t SHADOW_MAX   = 256;
+
+void set_error(const char *fmt, ...) {
+    char tmp[512];
+    va_list ap; va_start(ap, fmt); vsnprintf(tmp, sizeof tmp, fmt, ap); va_end(ap);
+    if (g.last_error.empty()) g.last_error = tmp;      // sticky: keep the first
+    fprintf(stderr, "thvm_cuda: %s\n", tmp);
+}
+void fatal(const char *fmt, ...) {
+    char tmp[512];
+    va_list ap; va_start(ap, fmt); vsnprintf(tmp, sizeof tmp, fmt, ap); va_end(ap);
+    fprintf(stderr, "thvm_cuda: FATAL: %s\n", tmp);
+    exit(1);   // the reference's backends exit on unrecoverable errors too (src/backend/metal/pool.m:49-53)
+}
+
+Buf &buf_checked(uint32_t id, const char *who) {
+    if (!g.ready) fatal("%s: backend not initialised (no CUDA device?)", who);
+    if (id == 0 || id >= THC_MAX_BUFS || g.bufs[id].ptr == nullptr)
+        fatal("%s: buffer id %u is not live", who, id);
+    return g.bufs[id];
+}
+
+void *scratch_reserve(uint64_t bytes) {
+    if (bytes <= g.scratch_bytes) return g.scratch;
+    if (g.scratch) THC_CUDA_OK(cudaFreeAsync(g.scratch, g.stream));
+    uint64_t want = bytes + (bytes >> 2);
+    THC_CUDA_OK(cudaMallocAsync(&g.scratch, want, g.stream));
+    g.scratch_bytes = want;
+    return g.scratch;
+}
+
+// ---- per-family launch statistics (profile_report) ----
+struct PlanStat { uint64_t launches = 0; double ms = 0; };
+static std::map<std::string, PlanStat> *plan_stats = nullptr;
+static cudaEvent_t prof_ev[2] = {nullptr, nullptr};
+static bool prof_open = false;
+
+void after_launch(const char *plan) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) fatal("launch of %s failed: %s", plan, cudaGetErrorString(e));
+    g.launches++;
+    g.last_plan = plan;
+    if (g.profile) {
+        if (!plan_stats) plan_stats = new std::map<std::string, PlanStat>();
+        PlanStat &s = (*plan_stats)[plan];
+        s.launches++;
+        if (prof_open) {           // close the bracket opened by profile_begin
+            THC_CUDA_OK(cudaEventRecord(prof_ev[1], g.stream));
+            THC_CUDA_OK(cudaEventSynchronize(prof_ev[1]));
+            float ms = 0; THC_CUDA_OK(cudaEventElapsedTime(&ms, prof_ev[0], prof_ev[1]));
+            s.ms += ms; prof_open = false;
+        }
+    }
+}
+void profile_begin() {             // called by dispatchers right before a launch when profiling
+    if (!g.profile) return;
+    if (!prof_ev[0]) { cudaEventCreate(&prof_ev[0]); cudaEventCreate(&prof_ev[1]); }
+    THC_CUDA_OK(cudaEventRecord(prof_ev[0], g.stream));
+    prof_open = true;
+}
+
+static void check_device_status(const char *who) {
+    int st = 0;
+    THC_CUDA_OK(cudaMemcpyAsync(&st, g.dev_status, sizeof st, cudaMemcpyDeviceToHost, g.stream));
+    THC_CUDA_OK(cudaStreamSynchronize(g.stream));
+    if (st) {
+        set_error("%s: device status 0x%x (1=load out of bounds, 2=store out of bounds, 4=bad program)", who, st);
+        THC_CUDA_OK(cudaMemsetAsync(g.dev_status, 0, sizeof(int), g.stream));
+    }
+}
+
+// ---- staging ring ----
+static uint8_t *ring_take(uint64_t bytes) {
+    const uint64_t half = g.ring_bytes / 2;
+    bytes = (bytes + 63) & ~63ull;
+    unsigned cur = (unsigned)(g.ring_pos / half);
+    if (g.ring_pos % half + bytes > half) {            // leave this half: fence it, enter the other
+        THC_CUDA_OK(cudaEventRecord(g.ring_half[cur], g.stream));
+        g.ring_half_pending[cur] = true;
+        cur ^= 1u;
+        if (g.ring_half_pending[cur]) {
+            THC_CUDA_OK(cudaEventSynchronize(g.ring_half[cur]));
+            g.ring_half_pending[cur] = false;
+        }
+        g.ring_pos = (uint64_t)cur * half;
+    }
+    uint8_t *p = g.ring + g.ring_pos;
+    g.ring_pos += bytes;
+    return p;
+}
+
+void upload_small(void *dev_dst, const void *src, uint64_t bytes) {
+    if (bytes > RING_MAX_MSG) fatal("upload_small: %llu bytes", (unsigned long long)bytes);
+    uint8_t *stage = ring_take(bytes);
+    memcpy(stage, src, bytes);
+    THC_CUDA_OK(cudaMemcpyAsync(dev_dst, stage, bytes, cudaMemcpyHostToDevice, g.stream));
+}
+
+}  // namespace thc
+
+using namespace thc;
+
+extern "C" {
+
+int thvm_cuda_init(void) {
+    if (g.ready) thvm_cuda_shutdown();
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        set_error("init: no CUDA device");
+        return 1;
+    }
+    const char *ev = getenv("THVM_CUDA_DEVICE");
+    if (!ev) ev = getenv("LOCAL_RANK");
+    int dev = ev ? atoi(ev) : 0;
+    if (dev < 0 || dev >= n) dev = dev % n;
+    if (cudaSetDevice(dev) != cudaSuccess) { set_error("init: cudaSetDevice(%d) failed", dev); return 1; }
+    cudaDeviceProp prop;
+    THC_CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major < 10) {
+        set_error("init: device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+        return 1;
+    }
+    g.device = dev;
+    g.sm_count = prop.multiProcessorCount;
+    THC_CUDA_OK(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+    cudaMemPool_t mp;
+    THC_CUDA_OK(cudaDeviceGetDefaultMemPool(&mp, dev));
+    uint64_t keep_all = UINT64_MAX;
+    THC_CUDA_OK(cudaMemPoolSetAttribute(mp, cudaMemPoolAttrReleaseThreshold, &keep_all));
+    THC_CUDA_OK(cudaHostAlloc((void **)&g.ring, RING_BYTES, cudaHostAllocDefault));
+    g.ring_bytes = RING_BYTES; g.ring_pos = 0;
+    for (int i = 0; i < 2; i++) {
+        THC_CUDA_OK(cudaEventCreateWithFlags(&g.ring_half[i], cudaEventDisableTiming));
+        g.ring_half_pending[i] = false;
+    }
+    THC_CUDA_OK(cudaMalloc((void **)&g.dev_status, sizeof(int)));
+    THC_CUDA_OK(cudaMemset(g.dev_status, 0, sizeof(int)));
+    for (uint32_t i = 0; i < THC_MAX_BUFS; i++) g.bufs[i] = Buf();
+    g.count = 1; g.persistent = 0;
+    g.scratch = nullptr; g.scratch_bytes = 0;
+    g.launches = 0; g.last_plan = ""; g.last_error.clear();
+    g.profile = getenv("THVM_PROFILE") != nullptr;
+    g.ready = true;
+    return 0;
+}
+
+static void release(uint32_t id) {
+    Buf &b = g.bufs[id];
+    if (b.ptr) THC_CUDA_OK(cudaFreeAsync(b.ptr, g.stream));
+    free(b.shadow);
+    b = Buf();
+}
+
+void plan_cache_clear(void);   // plan.cu
+
+void thvm_cuda_shutdown(void) {
+    if (!g.ready) return;
+    cudaStreamSynchronize(g.stream);
+    for (uint32_t i = 1; i < g.count; i++) if (g.bufs[i].ptr) release(i);
+    plan_cache_clear();
+    if (g.scratch) cudaFreeAsync(g.scratch, g.stream);
+    g.scratch = nullptr; g.scratch_bytes = 0;
+    cudaStreamSynchronize(g.stream);
+    cudaFree(g.dev_status); g.dev_status = nullptr;
+    cudaFreeHost(g.ring); g.ring = nullptr;
+    for (int i = 0; i < 2; i++) { cudaEventDestroy(g.ring_half[i]); g.ring_half[i] = nullptr; }
+    cudaStreamDestroy(g.stream); g.stream = nullptr;
+    g.count = 1;
+    g.ready = false;
+}
+
+uint32_t thvm_cuda_buf_alloc(uint64_t bytes) {
+    if (!g.ready) fatal("buf_alloc: backend not initialised (no CUDA device?)");
+    if (g.count >= THC_MAX_BUFS) { set_error("buf_alloc: id space exhausted (%u)", THC_MAX_BUFS); return 0; }
+    uint64_t sz = (bytes + 15) & ~15ull;
+    if (sz == 0) sz = 16;
+    void *p = nullptr;
+    cudaError_t e = cudaMallocAsync(&p, sz, g.stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+        return 0;
+    }
+    THC_CUDA_OK(cudaMemsetAsync(p, 0, sz, g.stream));
+    uint32_t id = g.count++;
+    Buf &b = g.bufs[id];
+    b.ptr = p; b.bytes = bytes; b.refcount = 1;
+    if (bytes <= SHADOW_MAX) {
+        b.shadow = (uint8_t *)calloc(1, SHADOW_MAX);
+        b.shadow_valid = true;                     // zeros, like the device copy
+    }
+    return id;
+}
+
+void thvm_cuda_buf_free(uint32_t id) {
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    release(id);
+}
+
+void thvm_cuda_buf_incref(uint32_t id) {
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    g.bufs[id].refcount++;
+}
+
+void thvm_cuda_buf_decref(uint32_t id) {
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    if (id <= g.persistent) return;
+    Buf &b = g.bufs[id];
+    if (b.refcount > 0) b.refcount--;
+    if (b.refcount == 0) release(id);
+}
+
+void thvm_cuda_mem_checkpoint(uint32_t *leaf_buf_ids, uint32_t n_leaves) {
+    (void)leaf_buf_ids; (void)n_leaves;   // stream-ordered frees need no checkpoint
+}
+void thvm_cuda_buf_mark_use(uint32_t id) { (void)id; }
+
+void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
+    Buf &b = buf_checked(id, "buf_write");
+    if (bytes > b.bytes) {
+        set_error("buf_write: %llu bytes into buffer %u of %llu", (unsigned long long)bytes, id, (unsigned long long)b.bytes);
+        bytes = b.bytes;
+    }
+    if (bytes == 0) return;
+    if (b.shadow) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
+    if (bytes <= RING_MAX_MSG) {
+        uint8_t *stage = ring_take(bytes);
+        memcpy(stage, data, bytes);
+        THC_CUDA_OK(cudaMemcpyAsync(b.ptr, stage, bytes, cudaMemcpyHostToDevice, g.stream));
+    } else {
+        // Large payloads go straight from the caller's memory (full PCIe rate
+        // when it is pinned) and the call waits for the DMA, after which the
+        // caller may reuse the source.
+        THC_CUDA_OK(cudaMemcpyAsync(b.ptr, data, bytes, cudaMemcpyHostToDevice, g.stream));
+        THC_CUDA_OK(cudaStreamSynchronize(g.stream));
+    }
+}
+
+static void read_impl(uint32_t id, void *out, uint64_t bytes, bool sync) {
+    Buf &b = buf_checked(id, "buf_read");
+    uint64_t n = bytes < b.bytes ? bytes : b.bytes;
+    if (bytes > n) memset((uint8_t *)out + n, 0, bytes - n);   // past the end reads as zero (src/backend/metal/pool.m:214-218)
+    if (n == 0) return;
+    if (b.shadow && b.shadow_valid) { memcpy(out, b.shadow, n); return; }
+    THC_CUDA_OK(cudaMemcpyAsync(out, b.ptr, n, cudaMemcpyDeviceToHost, g.stream));
+    if (sync) check_device_status("buf_read");                // drains the stream
+}
+void thvm_cuda_buf_read(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, true); }
+// The copy is still stream-ordered after the kernels that produced the data;
+// only the final wait is left to the caller (thvm_cuda_sync).
+void thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, false); }
+
+void thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes) {
+    Buf &d = buf_checked(dst_buf, "buf_copy(dst)");
+    Buf &s = buf_checked(src_buf, "buf_copy(src)");
+    uint64_t n = nbytes;
+    if (n > d.bytes || n > s.bytes) {
+        set_error("buf_copy: %llu bytes exceed dst %llu / src %llu", (unsigned long long)n,
+                  (unsigned long long)d.bytes, (unsigned long long)s.bytes);
+        n = d.bytes < s.bytes ? d.bytes : s.bytes;
+    }
+    if (n == 0) return;
+    THC_CUDA_OK(cudaMemcpyAsync(d.ptr, s.ptr, n, cudaMemcpyDeviceToDevice, g.stream));
+    if (d.shadow && s.shadow && s.shadow_valid) { memcpy(d.shadow, s.shadow, n); d.shadow_valid = true; }
+    else d.shadow_valid = false;
+}
+
+void thvm_cuda_pool_reset(uint32_t keep) {
+    if (!g.ready) return;
+    uint32_t first = keep + 1;
+    if (first < 1) first = 1;
+    for (uint32_t i = first; i < g.count; i++) if (g.bufs[i].ptr) release(i);
+    if (first < g.count) g.count = first;
+}
+
+void thvm_cuda_pool_set_persistent(uint32_t max_buf) { g.persistent = max_buf; }
+
+void thvm_cuda_begin_batch(void) {}
+void thvm_cuda_end_batch(void) {}   // one stream already orders and batches the work
+
+void thvm_cuda_profile_report(void) {
+    if (!plan_stats) { fprintf(stderr, "thvm_cuda profile: no launches recorded (set THVM_PROFILE=1 before init)\n"); return; }
+    fprintf(stderr, "thvm_cuda profile: %-22s %10s %12s\n", "kernel family", "launches", "gpu ms");
+    for (auto &kv : *plan_stats)
+        fprintf(stderr, "thvm_cuda profile: %-22s %10llu %12.3f\n", kv.first.c_str(),
+                (unsigned long long)kv.second.launches, kv.second.ms);
+}
+void thvm_cuda_profile_reset(void) { if (plan_stats) plan_stats->clear(); g.launches = 0; }
+
+const char *thvm_cuda_last_error(void) {
+    if (g.ready && g.last_error.empty()) check_device_status("last_error");
+    return g.last_error.c_str();
+}
+void thvm_cuda_clear_error(void) { g.last_error.clear(); }
+void *thvm_cuda_stream(void) { return (void *)g.stream; }
+void thvm_cuda_sync(void) { if (g.ready) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
+void *thvm_cuda_buf_ptr(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS) ? g.bufs[id].ptr : nullptr; }
+uint64_t thvm_cuda_buf_bytes(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS && g.bufs[id].ptr) ? g.bufs[id].bytes : 0; }
+uint64_t thvm_cuda_launch_count(void) { return g.launches; }
+const char *thvm_cuda_last_plan(void) { return g.last_plan; }
+void thvm_cuda_set_force_generic(int on) { g.force_generic = on; }
+
+}  // extern "C"

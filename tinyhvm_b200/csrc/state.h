@@ -1,0 +1,86 @@
+// state.h — process-global state of the backend (host side).
+//
+// The reference's vtable carries no context pointer and its backends keep
+// file-scope state (src/backend/cpu/pool.c:6-10), so this library does too:
+// one process, one GPU, one stream.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string>
+#include "../../include/thvm_cuda.h"
+
+namespace thc {
+
+struct Buf {
+    void    *ptr      = nullptr;   // device memory
+    uint64_t bytes    = 0;         // size asked for by the caller
+    uint32_t refcount = 0;
+    uint8_t *shadow   = nullptr;   // host copy of a small host-written buffer
+    bool     shadow_valid = false; // false once a kernel or copy wrote the buffer
+};
+
+struct State {
+    bool         ready = false;
+    int          device = 0;
+    int          sm_count = 148;
+    cudaStream_t stream = nullptr;
+    Buf          bufs[THC_MAX_BUFS];
+    uint32_t     count = 1;          // next id; 0 is the null buffer
+    uint32_t     persistent = 0;     // ids <= this survive decref
+    // pinned staging ring for small host->device writes
+    uint8_t     *ring = nullptr;
+    uint64_t     ring_bytes = 0, ring_pos = 0;
+    cudaEvent_t  ring_half[2] = {nullptr, nullptr};
+    bool         ring_half_pending[2] = {false, false};
+    // pinned bounce buffer for reads
+    uint8_t     *bounce = nullptr;
+    uint64_t     bounce_bytes = 0;
+    // device status word raised by kernels (load/store out of bounds ...)
+    int         *dev_status = nullptr;
+    // library-owned scratch (two-pass reductions, operand splits); grow-only
+    void        *scratch = nullptr;
+    uint64_t     scratch_bytes = 0;
+    // bookkeeping
+    uint64_t     launches = 0;
+    const char  *last_plan = "";
+    int          force_generic = 0;
+    std::string  last_error;
+    // profiling (THVM_PROFILE / profile_report)
+    bool         profile = false;
+};
+
+extern State g;
+
+void set_error(const char *fmt, ...);
+[[noreturn]] void fatal(const char *fmt, ...);
+
+#define THC_CUDA_OK(expr)                                                         \
+    do {                                                                          \
+        cudaError_t _e = (expr);                                                  \
+        if (_e != cudaSuccess)                                                    \
+            ::thc::fatal("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),  \
+                         __FILE__, __LINE__);                                     \
+    } while (0)
+
+// a live buffer or a fatal error
+Buf &buf_checked(uint32_t id, const char *who);
+// scratch of at least `bytes` (stream-ordered reuse: all users run on g.stream)
+void *scratch_reserve(uint64_t bytes);
+// mark a buffer as written by the device
+inline void mark_device_written(uint32_t id) { g.bufs[id].shadow_valid = false; }
+// grid size helper: enough CTAs to fill the machine `waves` times over
+inline unsigned grid_for(uint64_t work_items, unsigned per_cta, unsigned max_ctas_per_sm = 16) {
+    uint64_t need = (work_items + per_cta - 1) / per_cta;
+    uint64_t cap  = (uint64_t)g.sm_count * max_ctas_per_sm;
+    if (need < 1) need = 1;
+    return (unsigned)(need < cap ? need : cap);
+}
+// bracket a launch: profile_begin() before, after_launch() after
+void profile_begin();
+void after_launch(const char *plan);
+// host -> device copy of a small block through the pinned staging ring
+void upload_small(void *dev_dst, const void *src, uint64_t bytes);
+
+}  // namespace thc
