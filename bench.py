@@ -266,7 +266,7 @@ def main():
     a, b, c = arrays
     probe = slice(0, 4 * COLS)
     u = a[probe] * b[probe] + c[probe]
-    ok_g = np.array_equal(g[probe], np.where(u > 0, b[probe], np.float32(0)) * np.float32(1.0) + np.float32(0))
+    ok_g = np.array_equal(g[probe], np.where(u > 0, b[probe], np.float32(0)))
     y_ref = np.maximum(u, 0).reshape(4, COLS).astype(np.float64).sum(axis=1)
     ok_y = np.allclose(y[:4], y_ref, rtol=1e-5)
     err = be.last_error()

@@ -27,8 +27,24 @@ def is_contraction(d):
     return d.reduce_type == SUM and len(d.ops) == 1 and d.ops[0][0] == MUL and len(d.leaves) == 2
 
 
-def check(d, got, want, strict_serial=False):
-    """Compare one dispatch's output with the oracle's under the stated tolerances."""
+def abs_sum(oracle, d):
+    """Sum of |terms| per output of a SUM dispatch, from the oracle itself: the
+    same dispatch with |x| = MAX(x, NEG(x)) appended to the op list."""
+    if oracle is None or d.reduce_type != SUM or d.post_start or len(d.ops) + 2 > abi.MAX_OPS:
+        return None
+    nl, no = len(d.leaves), len(d.ops)
+    last = nl + no - 1 if no else 0
+    ops = list(d.ops) + [(abi.NEG, last, last), (abi.MAX, last, nl + no)]
+    d2 = abi.Dispatch(d.leaves, ops, d.full, d.reduce_axes, SUM, F32)
+    return oracle.run(d2).astype(np.float64)
+
+
+def check(d, got, want, strict_serial=False, oracle=None):
+    """Compare one dispatch's output with the oracle's under the stated tolerances.
+
+    For a re-ordered SUM the oracle's own left-to-right f32 accumulation is a
+    rounding distance of up to ~sqrt(n)*eps*sum|terms| away from the exact sum,
+    so that distance (x2, for the two orders) is added to the 1e-5 relative bound."""
     inexact_ops = any(o[0] in (EXP, LOG) for o in d.ops)
     red_n = int(np.prod([d.full[a] for a in d.reduce_axes])) if d.reduce_type else 1
     reordered = d.reduce_type == SUM and d.out_dtype == F32 and (red_n > 64 or not strict_serial)
@@ -39,14 +55,21 @@ def check(d, got, want, strict_serial=False):
     finite = np.isfinite(w)
     assert np.array_equal(np.isnan(g), np.isnan(w)) or d.out_dtype != F32 or inexact_ops, f"{d.name}: NaN pattern differs"
     if d.out_dtype in (I32, U32):
-        assert np.max(np.abs(g - w)) <= 1 + 1e-5 * np.max(np.abs(w)), d.name    # a truncated value may sit on an integer boundary
+        # only reached with EXP/LOG in the chain: a value that sits on an integer
+        # boundary may truncate differently after a 1-ulp libm difference
+        assert np.mean(g != w) <= 0.02, f"{d.name}: {np.mean(g != w):.3f} of the integer outputs differ"
         return
     rtol = 1e-4 if is_contraction(d) else 1e-5
     if d.out_dtype == F16:
         rtol = 1e-3                                                             # one half-precision ulp
     rms = float(np.sqrt(np.mean(w[finite] ** 2))) if finite.any() else 0.0
     err = np.abs(g[finite] - w[finite])
-    bound = rtol * np.abs(w[finite]) + rtol * rms + 1e-30
+    bound = rtol * np.abs(w[finite]) + 1e-30
+    S = abs_sum(oracle, d) if reordered else None
+    if S is not None and np.all(np.isfinite(S)):
+        bound = bound + 2.0 * np.sqrt(red_n) * 6e-8 * S[finite]
+    else:
+        bound = bound + rtol * rms
     assert np.all(err <= bound), f"{d.name}: max excess {np.max(err / bound):.2f}x over rtol {rtol}"
     assert np.array_equal(g[~finite], w[~finite], equal_nan=True) or inexact_ops, d.name
 
@@ -58,7 +81,7 @@ def test_named_and_fuzzed_dispatches(cuda, oracle, generic):
         plans = {}
         for d in all_cases():
             got, want = cuda.run(d), oracle.run(d)
-            check(d, got, want, strict_serial=generic)
+            check(d, got, want, strict_serial=generic, oracle=oracle)
             plans[cuda.last_plan()] = plans.get(cuda.last_plan(), 0) + 1
         print("plans used:", plans)
         assert cuda.last_error() == ""
@@ -74,10 +97,10 @@ def test_reference_golden_vectors_on_gpu(cuda):
         assert same(cuda.run(d), want), name
 
 
-def test_committed_fixtures_on_gpu(cuda):
+def test_committed_fixtures_on_gpu(cuda, oracle):
     z = np.load(GOLDEN / "boundary_cases.npz")
     for key, d in golden_case_list():
-        check(d, cuda.run(d), z[key])
+        check(d, cuda.run(d), z[key], oracle=oracle)
 
 
 def test_pool_contract(cuda):

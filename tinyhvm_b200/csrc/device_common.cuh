@@ -105,6 +105,42 @@ __host__ __device__ __forceinline__ float roundtrip(float v, uint32_t dt) {
     }
 }
 
+// A stored element as raw bits (what memory holds after a store) and back.
+// u32/i32 -> f32 is not injective above 2^24, so an accumulator that lives in
+// a non-f32 output buffer has to be carried in this form.
+__host__ __device__ __forceinline__ uint32_t encode_bits(float v, uint32_t dt) {
+    switch (dt) {
+        case THC_F16: return f32_to_f16_bits(v);
+        case THC_I32: return (uint32_t)cast_i32(v);
+        case THC_U32: return cast_u32(v);
+        default: {
+#ifdef __CUDA_ARCH__
+            return __float_as_uint(v);
+#else
+            uint32_t b; memcpy(&b, &v, 4); return b;
+#endif
+        }
+    }
+}
+__host__ __device__ __forceinline__ float decode_bits(uint32_t b, uint32_t dt) {
+    switch (dt) {
+        case THC_F16: return f16_bits_to_f32((uint16_t)b);
+        case THC_I32: return (float)(int32_t)b;
+        case THC_U32: return (float)b;
+        default: {
+#ifdef __CUDA_ARCH__
+            return __uint_as_float(b);
+#else
+            float f; memcpy(&f, &b, 4); return f;
+#endif
+        }
+    }
+}
+__device__ __forceinline__ void store_bits(void *base, uint32_t dt, uint64_t i, uint32_t b) {
+    if (dt == THC_F16) ((uint16_t *)base)[i] = (uint16_t)b;
+    else ((uint32_t *)base)[i] = b;
+}
+
 // ---- scalar UOp ------------------------------------------------------------
 __device__ __forceinline__ float alu(uint32_t uop, uint32_t aux, float a, float b) {
     switch (uop) {

@@ -1,11 +1,464 @@
-// fast.cu — family selection for the specialised kernels.
+// fast.cu — the specialised bandwidth kernels and their selection.
+//
+// A dispatch (see plan.cu) qualifies when every leaf and the output are f32,
+// every leaf is a single view without compound masks, and each leaf dim equals
+// the iteration dim or is 1 (no modulo wrap).  Its iteration space is then
+// collapsed (fast_desc.h) and one of three skeletons runs it:
+//   k_ew         no reduce; each thread produces 4 consecutive outputs with
+//                128-bit loads/stores where the leaf layout allows it;
+//   k_red_inner  the innermost collapsed dim is reduced: 1, 32 or 256 threads
+//                cooperate on one output (warp shuffles, then shared memory);
+//                if there are too few outputs to fill 148 SMs the reduce range
+//                is split across CTAs and a second pass adds the partials
+//                (deterministic order, scratch from the library's pool);
+//   k_red_outer  the innermost collapsed dim is kept: threads run along it
+//                (coalesced) and walk the reduce range, same split scheme.
+// The fused op list is either interpreted per vector of 4 elements, or — for
+// the chains the training configs produce over and over (CHAINS below) —
+// compiled in, selected by matching the dispatch's op list, which is the part
+// of the reference's kernel-cache signature (src/tinyhvm.h:828-856) that does
+// not depend on shapes.
+//
+// Accumulation order differs from the CPU backend's left-to-right loop
+// (src/backend/cpu/dispatch.c:169-218): per-thread strided partial sums, then
+// a tree.  Elementwise results are bit-identical.
+#include <string.h>
+#include "device_common.cuh"
+#include "fast_desc.h"
 #include "plans.h"
 #include "state.h"
 
 namespace thc {
 
-void classify_plan(Plan *p) { p->kind = PLAN_GENERIC; }
-bool launch_fast(Plan *p, const GenArgs &args) { (void)p; (void)args; return false; }
-void free_fast(Plan *p) { (void)p; }
+// ------------------------------------------------------------------ static chains
+struct ChainDef { int nl, no; unsigned char uop[8], a[8], b[8]; };
+// unary ops carry b == a (the dispatcher canonicalises them the same way)
+constexpr ChainDef CHAINS[] = {
+    {0, 0, {}, {}, {}},                                                            // 0: interpreted
+    {3, 3, {THC_MUL, THC_ADD, THC_RELU}, {0, 3, 4}, {1, 2, 4}},                    // 1: relu(a*b+c)
+    {4, 4, {THC_MUL, THC_ADD, THC_CMP, THC_MUL}, {0, 4, 5, 1}, {1, 2, 3, 6}},      // 2: b*(a*b+c > z)
+    {2, 2, {THC_ADD, THC_RELU}, {0, 2}, {1, 2}},                                   // 3: relu(y+bias)
+    {2, 1, {THC_ADD}, {0}, {1}},                                                   // 4: a+b (pad / bias)
+    {2, 1, {THC_MUL}, {0}, {1}},                                                   // 5: a*b
+    {1, 0, {}, {}, {}},                                                            // 6: copy / plain reduce
+    {2, 1, {THC_SUB}, {0}, {1}},                                                   // 7: a-b
+    {2, 2, {THC_SUB, THC_EXP}, {0, 2}, {1, 2}},                                    // 8: exp(a-b)
+};
+constexpr int N_CHAINS = sizeof(CHAINS) / sizeof(CHAINS[0]);
+
+struct InterpEval {
+    static constexpr int MAXL = FL, NV = FL + FO;
+    __device__ static __forceinline__ int nleaves(const FProg &P) { return (int)P.n_leaves; }
+    __device__ static __forceinline__ int result(const FProg &P) { return P.n_ops ? (int)(P.n_leaves + P.n_ops - 1) : 0; }
+    template <int V>
+    __device__ static __forceinline__ void run(const FProg &P, float (&v)[NV][V]) {
+        const int nl = (int)P.n_leaves;
+        for (int i = 0; i < (int)P.n_ops; i++) {
+            const unsigned u = P.uop[i], x = P.aux[i];
+            const int a = P.a[i], b = P.b[i];
+#pragma unroll
+            for (int k = 0; k < V; k++) v[nl + i][k] = alu(u, x, v[a][k], v[b][k]);
+        }
+    }
+};
+
+template <int CI, int I, int V, int NV>
+struct ChainStep {
+    __device__ static __forceinline__ void run(float (&v)[NV][V]) {
+        constexpr ChainDef C = CHAINS[CI];
+        if constexpr (I < C.no) {
+            constexpr unsigned u = C.uop[I];
+            constexpr int a = C.a[I], b = C.b[I];
+#pragma unroll
+            for (int k = 0; k < V; k++) v[C.nl + I][k] = alu(u, 0u, v[a][k], v[b][k]);
+            ChainStep<CI, I + 1, V, NV>::run(v);
+        }
+    }
+};
+template <int CI>
+struct StaticEval {
+    static constexpr int MAXL = CHAINS[CI].nl, NV = CHAINS[CI].nl + CHAINS[CI].no;
+    __device__ static __forceinline__ int nleaves(const FProg &) { return CHAINS[CI].nl; }
+    __device__ static __forceinline__ int result(const FProg &) { return CHAINS[CI].no ? NV - 1 : 0; }
+    template <int V>
+    __device__ static __forceinline__ void run(const FProg &, float (&v)[NV][V]) { ChainStep<CI, 0, V, NV>::run(v); }
+};
+
+// ------------------------------------------------------------------ leaf access
+// V consecutive elements along the innermost collapsed dim, starting at coords c.
+template <int V>
+__device__ __forceinline__ void load_leaf(const FLeaf &L, const unsigned *c, int rank, float (&dst)[V]) {
+    long long off = L.off;
+    bool dead = false;
+#pragma unroll
+    for (int d = 0; d < FR; d++)
+        if (d < rank) {
+            off += (long long)c[d] * L.stride[d];
+            if (d < rank - 1 && ((L.masked >> d) & 1u) && (c[d] < L.mlo[d] || c[d] >= L.mhi[d])) dead = true;
+        }
+    if (dead) {
+#pragma unroll
+        for (int k = 0; k < V; k++) dst[k] = 0.0f;
+        return;
+    }
+    const int in = rank - 1;
+    const bool inner_masked = (L.masked >> in) & 1u;
+    if (V == 4 && L.vec && !inner_masked) {
+        if (L.stride[in] == 1) {
+            const float4 q = *reinterpret_cast<const float4 *>(L.ptr + off);
+            dst[0] = q.x; dst[1] = q.y; dst[2] = q.z; dst[3] = q.w;
+        } else {
+            const float s = L.ptr[off];
+#pragma unroll
+            for (int k = 0; k < V; k++) dst[k] = s;
+        }
+        return;
+    }
+    const int si = L.stride[in];
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        const unsigned ci = c[in] + k;
+        dst[k] = (inner_masked && (ci < L.mlo[in] || ci >= L.mhi[in])) ? 0.0f : L.ptr[off + (long long)k * si];
+    }
+}
+
+template <class EV, int V>
+__device__ __forceinline__ void eval_at(const FDesc &D, const unsigned *c, float (&res)[V]) {
+    float v[EV::NV][V];
+    const int nl = EV::nleaves(D.prog);
+#pragma unroll
+    for (int i = 0; i < EV::MAXL; i++)
+        if (i < nl) load_leaf<V>(D.leaf[i], c, (int)D.rank, v[i]);
+    EV::template run<V>(D.prog, v);
+    const int r = EV::result(D.prog);
+#pragma unroll
+    for (int k = 0; k < V; k++) res[k] = v[r][k];
+}
+
+// ------------------------------------------------------------------ elementwise
+template <class EV, int V>
+__global__ void __launch_bounds__(256) k_ew(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    const unsigned long long items = D.numel / V;
+    const int rank = (int)D.rank;
+    for (unsigned long long it = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; it < items;
+         it += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long flat = it * V;
+        unsigned c[FR];
+        unsigned long long rem = flat;
+        for (int d = rank - 1; d > 0; d--) { c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+        c[0] = (unsigned)rem;
+        float res[V];
+        eval_at<EV, V>(D, c, res);
+        if (V == 4) *reinterpret_cast<float4 *>(out + flat) = make_float4(res[0], res[1], res[2], res[3]);
+        else out[flat] = res[0];
+    }
+}
+
+// ------------------------------------------------------------------ reduce, innermost dim reduced
+template <class EV, int G, int V>
+__global__ void __launch_bounds__(256) k_red_inner(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    __shared__ float part[8];
+    const int rank = (int)D.rank;
+    const unsigned rtype = D.rtype;
+    const unsigned long long items = D.n_red / V;
+    const unsigned long long chunk = (items + D.split - 1) / D.split;
+    const unsigned long long n_groups = D.n_out * D.split;
+    const unsigned lane = G == 1 ? 0u : threadIdx.x % G;
+    const unsigned long long stride_groups = ((unsigned long long)gridDim.x * blockDim.x) / G;
+    for (unsigned long long gi = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) / G; gi < n_groups;
+         gi += stride_groups) {
+        const unsigned long long o = gi / D.split;
+        const unsigned s = (unsigned)(gi % D.split);
+        unsigned c[FR];
+        {
+            unsigned long long rem = o;
+            for (int k = (int)D.n_k - 1; k >= 0; k--) { const unsigned d = D.kd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+        }
+        const unsigned long long lo = (unsigned long long)s * chunk;
+        const unsigned long long hi = lo + chunk < items ? lo + chunk : items;
+        float acc = red_init(rtype);
+        for (unsigned long long it = lo + lane; it < hi; it += G) {
+            unsigned long long rem = it * V;
+            for (int k = (int)D.n_r - 1; k >= 0; k--) { const unsigned d = D.rd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+            float res[V];
+            eval_at<EV, V>(D, c, res);
+#pragma unroll
+            for (int k = 0; k < V; k++) acc = red_combine(rtype, acc, res[k]);
+        }
+        if (G > 1) {
+#pragma unroll
+            for (int w = 16; w > 0; w >>= 1) acc = red_combine(rtype, acc, __shfl_down_sync(0xffffffffu, acc, w));
+        }
+        if (G == 256) {
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            if (threadIdx.x == 0) { acc = part[0]; for (int w = 1; w < 8; w++) acc = red_combine(rtype, acc, part[w]); }
+        }
+        if (lane == 0) out[gi] = acc;       // gi == o when split == 1
+    }
+}
+
+// ------------------------------------------------------------------ reduce, innermost dim kept
+template <class EV>
+__global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    __shared__ float part[8][33];
+    const int rank = (int)D.rank;
+    (void)rank;
+    const unsigned rtype = D.rtype;
+    const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const unsigned long long o = (unsigned long long)blockIdx.x * 32 + tx;
+    const bool live = o < D.n_out;
+    unsigned c[FR];
+#pragma unroll
+    for (int d = 0; d < FR; d++) c[d] = 0;
+    if (live) {
+        unsigned long long rem = o;
+        for (int k = (int)D.n_k - 1; k >= 0; k--) { const unsigned d = D.kd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+    }
+    float acc = red_init(rtype);
+    if (live)
+        for (unsigned long long r = (unsigned long long)blockIdx.y * 8 + ty; r < D.n_red; r += 8ull * gridDim.y) {
+            unsigned long long rem = r;
+            for (int k = (int)D.n_r - 1; k >= 0; k--) { const unsigned d = D.rd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+            float res[1];
+            eval_at<EV, 1>(D, c, res);
+            acc = red_combine(rtype, acc, res[0]);
+        }
+    part[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && live) {
+        for (int w = 1; w < 8; w++) acc = red_combine(rtype, acc, part[w][tx]);
+        out[o * gridDim.y + blockIdx.y] = acc;
+    }
+}
+
+// second pass: out[o] = fold of partial[o*split .. o*split+split)
+__global__ void __launch_bounds__(256) k_red_final(const float *__restrict__ partial, float *__restrict__ out,
+                                                   unsigned long long n_out, unsigned split, unsigned rtype) {
+    for (unsigned long long o = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; o < n_out;
+         o += (unsigned long long)gridDim.x * blockDim.x) {
+        float acc = partial[o * split];
+        for (unsigned s = 1; s < split; s++) acc = red_combine(rtype, acc, partial[o * split + s]);
+        out[o] = acc;
+    }
+}
+
+// ------------------------------------------------------------------ host: classify
+struct FastDesc {
+    FDesc d;
+    int   strategy;                 // 0 ew, 1 reduce-inner, 2 reduce-outer
+    int   group;                    // threads per output for reduce-inner
+    long long min_off[FL], max_off[FL];
+    const char *name;
+};
+
+static bool build_fast(const GenDesc &H, FastDesc &F) {
+    if (H.post_start || H.n_leaves > FL || H.n_ops > FO || H.out_dtype != THC_F32 || H.full_numel == 0) return false;
+    const int rank = (int)H.rank;
+    long long st[FL][THC_MAX_DIM];
+    unsigned lo[FL][THC_MAX_DIM], hi[FL][THC_MAX_DIM];
+    bool part[FL][THC_MAX_DIM];
+    for (unsigned i = 0; i < H.n_leaves; i++) {
+        const DLeaf &L = H.leaves[i];
+        if (L.tracker >= 0 || L.dtype != THC_F32) return false;
+        if (L.v.has_mask && L.v.n_cm) return false;
+        const int n = (int)L.v.rank < rank ? (int)L.v.rank : rank;
+        for (int d = 0; d < rank; d++) {
+            st[i][d] = 0; lo[i][d] = 0; hi[i][d] = H.full_dims[d]; part[i][d] = false;
+            if (d >= n) continue;
+            const unsigned ld = L.v.dims[d];
+            if (ld == 0 || (ld != H.full_dims[d] && ld != 1)) return false;
+            st[i][d] = ld > 1 ? L.v.strides[d] : 0;
+            if (L.v.has_mask) {
+                lo[i][d] = L.v.mb[d];
+                hi[i][d] = L.v.me[d] < H.full_dims[d] ? L.v.me[d] : H.full_dims[d];
+                part[i][d] = lo[i][d] > 0 || hi[i][d] < H.full_dims[d];
+                if (hi[i][d] <= lo[i][d]) return false;            // leaf is zero everywhere: leave to the generic kernel
+            }
+        }
+    }
+    // collapse
+    struct Dim { unsigned long long n; bool red; int src; };
+    Dim dims[THC_MAX_DIM]; int nd = 0;
+    long long cst[FL][THC_MAX_DIM]; unsigned clo[FL][THC_MAX_DIM], chi[FL][THC_MAX_DIM]; bool cpart[FL][THC_MAX_DIM];
+    for (int d = 0; d < rank; d++) {
+        if (H.full_dims[d] == 1) {
+            for (unsigned i = 0; i < H.n_leaves; i++) if (part[i][d]) return false;
+            continue;
+        }
+        const bool red = H.has_reduce && [&] { for (unsigned k = 0; k < H.n_rdims; k++) if ((int)H.rdim[k] == d) return true; return false; }();
+        bool merge = nd > 0 && dims[nd - 1].red == red;
+        if (merge)
+            for (unsigned i = 0; i < H.n_leaves && merge; i++)
+                if (cpart[i][nd - 1] || part[i][d] || cst[i][nd - 1] != st[i][d] * (long long)H.full_dims[d]) merge = false;
+        if (merge && dims[nd - 1].n * H.full_dims[d] > 0xFFFFFFFFull) merge = false;
+        if (merge) {
+            dims[nd - 1].n *= H.full_dims[d];
+            for (unsigned i = 0; i < H.n_leaves; i++) { cst[i][nd - 1] = st[i][d]; clo[i][nd - 1] = 0; chi[i][nd - 1] = (unsigned)dims[nd - 1].n; }
+        } else {
+            dims[nd] = {H.full_dims[d], red, d};
+            for (unsigned i = 0; i < H.n_leaves; i++) { cst[i][nd] = st[i][d]; clo[i][nd] = lo[i][d]; chi[i][nd] = hi[i][d]; cpart[i][nd] = part[i][d]; }
+            nd++;
+        }
+    }
+    if (nd == 0) {                                                // every dim is 1
+        dims[0] = {1, false, 0}; nd = 1;
+        for (unsigned i = 0; i < H.n_leaves; i++) { cst[i][0] = 0; clo[i][0] = 0; chi[i][0] = 1; cpart[i][0] = false; }
+    }
+    if (nd > FR) return false;
+
+    FDesc &D = F.d;
+    memset(&D, 0, sizeof D);
+    D.rank = nd; D.numel = 1; D.n_out = 1; D.n_red = 1;
+    D.rtype = H.has_reduce ? H.reduce_type : 0;
+    for (int d = 0; d < nd; d++) {
+        D.dims[d] = (unsigned)dims[d].n; D.is_red[d] = dims[d].red;
+        D.numel *= dims[d].n;
+        if (dims[d].red) { D.rd[D.n_r++] = d; D.n_red *= dims[d].n; } else { D.kd[D.n_k++] = d; D.n_out *= dims[d].n; }
+    }
+    const int in = nd - 1;
+    bool vec_ok = D.dims[in] % 4 == 0;
+    for (unsigned i = 0; i < H.n_leaves; i++) {
+        FLeaf &L = D.leaf[i];
+        L.off = H.leaves[i].v.offset;
+        F.min_off[i] = F.max_off[i] = L.off;
+        bool lv = true;
+        for (int d = 0; d < nd; d++) {
+            if (cst[i][d] > 0x7FFFFFFFll || cst[i][d] < -0x7FFFFFFFll) return false;
+            L.stride[d] = (int)cst[i][d]; L.mlo[d] = clo[i][d]; L.mhi[d] = chi[i][d];
+            if (cpart[i][d]) L.masked |= 1u << d;
+            const long long a = cst[i][d] * (long long)(cpart[i][d] ? clo[i][d] : 0);
+            const long long b = cst[i][d] * (long long)((cpart[i][d] ? chi[i][d] : D.dims[d]) - 1);
+            F.min_off[i] += a < b ? a : b;
+            F.max_off[i] += a < b ? b : a;
+            if (d != in && (cst[i][d] % 4) != 0) lv = false;
+        }
+        if (!(cst[i][in] == 1 || cst[i][in] == 0)) lv = false;
+        if (cst[i][in] == 1 && (L.off % 4) != 0) lv = false;
+        L.vec = lv ? 1u : 0u;
+    }
+    D.vec = vec_ok ? 4u : 1u;
+    D.split = 1;
+
+    // program; unary ops get b = a so they match the static chain table
+    D.prog.n_leaves = H.n_leaves; D.prog.n_ops = H.n_ops;
+    for (unsigned i = 0; i < H.n_ops; i++) {
+        const unsigned u = H.ops[i].uop;
+        const bool unary = u == THC_NEG || u == THC_EXP || u == THC_LOG || u == THC_RELU || u == THC_CAST || u == THC_SQRT;
+        D.prog.uop[i] = (unsigned char)u; D.prog.a[i] = (unsigned char)H.ops[i].arg_a;
+        D.prog.b[i] = (unsigned char)(unary ? H.ops[i].arg_a : H.ops[i].arg_b);
+        D.prog.aux[i] = (unsigned char)H.ops[i].aux;
+        if (u > 255 || H.ops[i].aux > 255) return false;
+    }
+    D.chain = 0;
+    for (int ci = 1; ci < N_CHAINS; ci++) {
+        const ChainDef &C = CHAINS[ci];
+        if (C.nl != (int)H.n_leaves || C.no != (int)H.n_ops) continue;
+        bool eq = true;
+        for (int k = 0; k < C.no && eq; k++)
+            eq = C.uop[k] == D.prog.uop[k] && C.a[k] == D.prog.a[k] && C.b[k] == D.prog.b[k] && D.prog.uop[k] != THC_CAST;
+        if (eq) { D.chain = ci; break; }
+    }
+
+    // strategy
+    const unsigned sms = (unsigned)g.sm_count;
+    if (!H.has_reduce) { F.strategy = 0; F.name = D.chain ? (D.vec == 4 ? "ew_vec4_static" : "ew_scalar_static") : (D.vec == 4 ? "ew_vec4_interp" : "ew_scalar_interp"); return true; }
+    if (D.is_red[in]) {
+        F.strategy = 1;
+        const unsigned long long items = D.n_red / D.vec;
+        F.group = items >= 1024 ? 256 : (items >= 32 ? 32 : 1);
+        if (F.group == 256 && D.n_out < 2ull * sms) {
+            unsigned long long want = (4ull * sms + D.n_out - 1) / D.n_out;
+            unsigned long long most = items / 1024;                 // keep >= 4 vectors per thread per slice
+            if (want > most) want = most;
+            if (want > 1) D.split = (unsigned)want;
+        }
+        F.name = F.group == 256 ? (D.split > 1 ? "reduce_inner_cta_split" : "reduce_inner_cta") : (F.group == 32 ? "reduce_inner_warp" : "reduce_inner_thread");
+        return true;
+    }
+    F.strategy = 2;
+    D.vec = 1;
+    const unsigned long long gx = (D.n_out + 31) / 32;
+    if (gx > 0x7FFFFFFFull) return false;
+    unsigned long long want = gx < 2ull * sms ? (2ull * sms + gx - 1) / gx : 1;
+    unsigned long long most = (D.n_red + 31) / 32;
+    if (want > most) want = most;
+    if (want > 65535) want = 65535;
+    D.split = want > 1 ? (unsigned)want : 1u;
+    F.name = D.split > 1 ? "reduce_outer_split" : "reduce_outer";
+    return true;
+}
+
+void classify_plan(Plan *p) {
+    FastDesc *F = new FastDesc();
+    if (build_fast(p->host, *F)) { p->fast = (struct FastDesc *)F; p->kind = F->strategy == 0 ? PLAN_EW : PLAN_REDUCE; }
+    else { delete F; p->fast = nullptr; p->kind = PLAN_GENERIC; }
+}
+void free_fast(Plan *p) { delete (FastDesc *)p->fast; p->fast = nullptr; }
+
+// ------------------------------------------------------------------ host: launch
+template <class EV>
+static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
+    const unsigned long long items = D.numel / D.vec;
+    if (F.strategy == 0) {
+        const unsigned grid = grid_for(items, 256, 8);
+        if (D.vec == 4) k_ew<EV, 4><<<grid, 256, 0, g.stream>>>(D, out);
+        else            k_ew<EV, 1><<<grid, 256, 0, g.stream>>>(D, out);
+        return;
+    }
+    float *dst = out;
+    if (D.split > 1) dst = (float *)scratch_reserve(D.n_out * D.split * sizeof(float));
+    if (F.strategy == 1) {
+        const unsigned long long groups = D.n_out * D.split;
+        if (F.group == 256) {
+            const unsigned grid = grid_for(groups, 1, 8);
+            if (D.vec == 4) k_red_inner<EV, 256, 4><<<grid, 256, 0, g.stream>>>(D, dst);
+            else            k_red_inner<EV, 256, 1><<<grid, 256, 0, g.stream>>>(D, dst);
+        } else if (F.group == 32) {
+            const unsigned grid = grid_for(groups, 8, 8);
+            if (D.vec == 4) k_red_inner<EV, 32, 4><<<grid, 256, 0, g.stream>>>(D, dst);
+            else            k_red_inner<EV, 32, 1><<<grid, 256, 0, g.stream>>>(D, dst);
+        } else {
+            const unsigned grid = grid_for(groups, 256, 8);
+            if (D.vec == 4) k_red_inner<EV, 1, 4><<<grid, 256, 0, g.stream>>>(D, dst);
+            else            k_red_inner<EV, 1, 1><<<grid, 256, 0, g.stream>>>(D, dst);
+        }
+    } else {
+        dim3 grid((unsigned)((D.n_out + 31) / 32), D.split);
+        k_red_outer<EV><<<grid, 256, 0, g.stream>>>(D, dst);
+    }
+}
+
+bool launch_fast(Plan *p, const GenArgs &args) {
+    FastDesc &F = *(FastDesc *)p->fast;
+    FDesc D = F.d;
+    for (unsigned i = 0; i < D.prog.n_leaves; i++) {
+        // the leaf must stay inside its buffer; otherwise the checked generic kernel runs
+        if (F.min_off[i] < 0 || (unsigned long long)F.max_off[i] >= args.cap[i]) return false;
+        D.leaf[i].ptr = (const float *)args.leaf[i];
+        if ((reinterpret_cast<uintptr_t>(args.leaf[i]) & 15u) != 0) D.leaf[i].vec = 0;
+    }
+    float *out = (float *)args.out;
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return false;
+    profile_begin();
+    switch (D.chain) {
+        case 1: launch_with<StaticEval<1>>(F, D, out); break;
+        case 2: launch_with<StaticEval<2>>(F, D, out); break;
+        case 3: launch_with<StaticEval<3>>(F, D, out); break;
+        case 4: launch_with<StaticEval<4>>(F, D, out); break;
+        case 5: launch_with<StaticEval<5>>(F, D, out); break;
+        case 6: launch_with<StaticEval<6>>(F, D, out); break;
+        case 7: launch_with<StaticEval<7>>(F, D, out); break;
+        case 8: launch_with<StaticEval<8>>(F, D, out); break;
+        default: launch_with<InterpEval>(F, D, out); break;
+    }
+    after_launch(F.name);
+    if (F.strategy != 0 && D.split > 1) {
+        k_red_final<<<grid_for(D.n_out, 256, 4), 256, 0, g.stream>>>((const float *)g.scratch, out, D.n_out, D.split, D.rtype);
+        after_launch("reduce_final");
+    }
+    return true;
+}
 
 }  // namespace thc

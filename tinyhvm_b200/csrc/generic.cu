@@ -166,7 +166,26 @@ __global__ void __launch_bounds__(256) k_generic_reduce(const GenDesc *__restric
             }
         }
         float acc = red_init(rtype);
-        if (G == 1 && odt != THC_F32) acc = roundtrip(acc, odt);
+        if (G == 1 && odt != THC_F32) {
+            // accumulate in the stored representation, as the CPU backend does by
+            // loading and storing the output element at every step
+            uint32_t bits = encode_bits(acc, odt);
+            for (uint64_t r = 0; r < n_red; r++) {
+                uint64_t rem = r;
+                for (int k = (int)D->n_rdims - 1; k >= 0; k--) {
+                    uint32_t d = D->rdim[k], dim = D->full_dims[d];
+                    c[d] = (uint32_t)(rem % dim); rem /= dim;
+                }
+                float v = eval_point(D, A, c, vals, n_eval);
+                bits = encode_bits(red_combine(rtype, decode_bits(bits, odt), v), odt);
+            }
+            for (uint32_t k = 0; k < D->n_rdims; k++) c[D->rdim[k]] = 0;
+            if (D->post_start && D->post_start < D->n_ops)
+                bits = encode_bits(post_reduce(D, A, c, vals, decode_bits(bits, odt)), odt);
+            if (oi < A.out_cap) store_bits(A.out, odt, oi, bits);
+            else atomicOr(A.status, ERR_STORE_OOB);
+            continue;
+        }
         for (uint64_t r = lane; r < n_red; r += G) {
             uint64_t rem = r;
             for (int k = (int)D->n_rdims - 1; k >= 0; k--) {
@@ -175,7 +194,6 @@ __global__ void __launch_bounds__(256) k_generic_reduce(const GenDesc *__restric
             }
             float v = eval_point(D, A, c, vals, n_eval);
             acc = red_combine(rtype, acc, v);
-            if (G == 1 && odt != THC_F32) acc = roundtrip(acc, odt);
         }
         if (G > 1) {
             for (int o = 16; o > 0; o >>= 1) acc = red_combine(rtype, acc, __shfl_down_sync(0xffffffffu, acc, o));
@@ -188,10 +206,7 @@ __global__ void __launch_bounds__(256) k_generic_reduce(const GenDesc *__restric
         }
         if (lane == 0) {
             for (uint32_t k = 0; k < D->n_rdims; k++) c[D->rdim[k]] = 0;
-            if (D->post_start && D->post_start < D->n_ops) {
-                float red = roundtrip(acc, odt);
-                acc = post_reduce(D, A, c, vals, red);
-            }
+            if (D->post_start && D->post_start < D->n_ops) acc = post_reduce(D, A, c, vals, acc);
             if (oi < A.out_cap) store_from_f32(A.out, odt, oi, acc);
             else atomicOr(A.status, ERR_STORE_OOB);
         }
