@@ -159,6 +159,13 @@ static f32 read_any(const void *buf, u32 dt, const thc_view_t *v, const thc_trac
     return leaf_value(buf, dt, v, c, rank);
 }
 
+/* Optional side channel for the tests: when non-NULL during a SUM dispatch, the
+ * f32 terms are also added in double precision into this array (one entry per
+ * output), giving the exactly-rounded sum the f32 orders can be measured
+ * against.  Not part of the reference's algorithm. */
+static double *wide_sums = NULL;
+void oracle_set_wide_sums(double *buf) { wide_sums = buf; }
+
 /* ---- the fused kernel: src/backend/cpu/dispatch.c:119-282 ---- */
 void oracle_dispatch_kernel_rs(void *out, const void *const *leaf_ptrs, const thc_view_t *const *leaf_views,
                                const thc_tracker_t *const *leaf_sts, u32 n_leaves,
@@ -176,6 +183,7 @@ void oracle_dispatch_kernel_rs(void *out, const void *const *leaf_ptrs, const th
     if (red) {                            /* dispatch.c:148-151 */
         f32 init = reduce->reduce_type == THC_RMAX ? -1e30f : 0.0f;
         for (u64 i = 0; i < n_out; i++) st(out, out_dtype, i, init);
+        if (wide_sums) for (u64 i = 0; i < n_out; i++) wide_sums[i] = 0.0;
     }
     u32 n_eval = (red && reduce->post_reduce_start) ? reduce->post_reduce_start : n_ops;
     f32 val[THC_MAX_LEAVES + THC_MAX_OPS];
@@ -191,6 +199,7 @@ void oracle_dispatch_kernel_rs(void *out, const void *const *leaf_ptrs, const th
             u64 oi = 0;
             for (u32 d = 0; d < rank; d++) oi += (u64)c[d] * keepw[d];
             f32 cur = ld(out, out_dtype, oi);
+            if (wide_sums && reduce->reduce_type == THC_SUM) wide_sums[oi] += (double)r;
             st(out, out_dtype, oi, reduce->reduce_type == THC_SUM ? cur + r : (r > cur ? r : cur));
         }
         for (i32 d = (i32)rank - 1; d >= 0; d--) {           /* row-major odometer */

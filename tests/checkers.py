@@ -49,6 +49,17 @@ class Oracle:
             ops, _u32(len(d.ops)), C.byref(full), C.byref(red) if red is not None else None, dts, _u32(d.out_dtype))
         return out[:d.out_numel]
 
+    def run_with_wide_sums(self, d: abi.Dispatch):
+        """(f32 output, the same SUM accumulated in double): the second is the
+        exact sum of the f32 terms, against which both summation orders are measured."""
+        wide = np.zeros(max(d.out_numel, 1), dtype=np.float64)
+        self.lib.oracle_set_wide_sums(_vp(wide.ctypes.data))
+        try:
+            out = self.run(d)
+        finally:
+            self.lib.oracle_set_wide_sums(None)
+        return out, wide[:d.out_numel]
+
     def signature(self, d: abi.Dispatch) -> int:
         views, sts, ops, full, red, _ = d.c_args()
         return int(self.lib.oracle_signature(ops, _u32(len(d.ops)), views, C.cast(sts, _vp) if sts is not None else None,

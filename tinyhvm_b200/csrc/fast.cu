@@ -135,6 +135,23 @@ __device__ __forceinline__ void eval_at(const FDesc &D, const unsigned *c, float
     for (int k = 0; k < V; k++) res[k] = v[r][k];
 }
 
+// ------------------------------------------------------------------ index decode
+// idx -> coordinates of the listed collapsed dims (outermost first).  The
+// outermost dim needs no division, and indices below 2^32 use 32-bit division.
+__device__ __forceinline__ void decode_dims(unsigned long long idx, const unsigned *list, int n,
+                                            const unsigned *dims, unsigned *c) {
+    if (n <= 0) return;
+    if (idx <= 0xFFFFFFFFull) {
+        unsigned rem = (unsigned)idx;
+        for (int k = n - 1; k > 0; k--) { const unsigned d = list[k]; const unsigned q = rem / dims[d]; c[d] = rem - q * dims[d]; rem = q; }
+        c[list[0]] = rem;
+    } else {
+        unsigned long long rem = idx;
+        for (int k = n - 1; k > 0; k--) { const unsigned d = list[k]; const unsigned long long q = rem / dims[d]; c[d] = (unsigned)(rem - q * dims[d]); rem = q; }
+        c[list[0]] = (unsigned)rem;
+    }
+}
+
 // ------------------------------------------------------------------ elementwise
 template <class EV, int V>
 __global__ void __launch_bounds__(256) k_ew(const __grid_constant__ FDesc D, float *__restrict__ out) {
@@ -144,9 +161,15 @@ __global__ void __launch_bounds__(256) k_ew(const __grid_constant__ FDesc D, flo
          it += (unsigned long long)gridDim.x * blockDim.x) {
         const unsigned long long flat = it * V;
         unsigned c[FR];
-        unsigned long long rem = flat;
-        for (int d = rank - 1; d > 0; d--) { c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
-        c[0] = (unsigned)rem;
+        if (flat <= 0xFFFFFFFFull) {
+            unsigned rem = (unsigned)flat;
+            for (int d = rank - 1; d > 0; d--) { const unsigned q = rem / D.dims[d]; c[d] = rem - q * D.dims[d]; rem = q; }
+            c[0] = rem;
+        } else {
+            unsigned long long rem = flat;
+            for (int d = rank - 1; d > 0; d--) { c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+            c[0] = (unsigned)rem;
+        }
         float res[V];
         eval_at<EV, V>(D, c, res);
         if (V == 4) *reinterpret_cast<float4 *>(out + flat) = make_float4(res[0], res[1], res[2], res[3]);
@@ -170,16 +193,31 @@ __global__ void __launch_bounds__(256) k_red_inner(const __grid_constant__ FDesc
         const unsigned long long o = gi / D.split;
         const unsigned s = (unsigned)(gi % D.split);
         unsigned c[FR];
-        {
-            unsigned long long rem = o;
-            for (int k = (int)D.n_k - 1; k >= 0; k--) { const unsigned d = D.kd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
-        }
+        decode_dims(o, D.kd, (int)D.n_k, D.dims, c);
         const unsigned long long lo = (unsigned long long)s * chunk;
         const unsigned long long hi = lo + chunk < items ? lo + chunk : items;
         float acc = red_init(rtype);
-        for (unsigned long long it = lo + lane; it < hi; it += G) {
-            unsigned long long rem = it * V;
-            for (int k = (int)D.n_r - 1; k >= 0; k--) { const unsigned d = D.rd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+        unsigned long long it = lo + lane;
+        if (G > 1) {
+            // two vectors per trip: twice the loads in flight per thread, two
+            // independent accumulation chains
+            float acc2 = red_init(rtype);
+            unsigned c2[FR];
+#pragma unroll
+            for (int d = 0; d < FR; d++) c2[d] = c[d];
+            for (; it + G < hi; it += 2 * G) {
+                decode_dims(it * V, D.rd, (int)D.n_r, D.dims, c);
+                decode_dims((it + G) * V, D.rd, (int)D.n_r, D.dims, c2);
+                float r1[V], r2[V];
+                eval_at<EV, V>(D, c, r1);
+                eval_at<EV, V>(D, c2, r2);
+#pragma unroll
+                for (int k = 0; k < V; k++) { acc = red_combine(rtype, acc, r1[k]); acc2 = red_combine(rtype, acc2, r2[k]); }
+            }
+            acc = red_combine(rtype, acc, acc2);
+        }
+        for (; it < hi; it += G) {
+            decode_dims(it * V, D.rd, (int)D.n_r, D.dims, c);
             float res[V];
             eval_at<EV, V>(D, c, res);
 #pragma unroll
@@ -213,14 +251,12 @@ __global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc
 #pragma unroll
     for (int d = 0; d < FR; d++) c[d] = 0;
     if (live) {
-        unsigned long long rem = o;
-        for (int k = (int)D.n_k - 1; k >= 0; k--) { const unsigned d = D.kd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+        decode_dims(o, D.kd, (int)D.n_k, D.dims, c);
     }
     float acc = red_init(rtype);
     if (live)
         for (unsigned long long r = (unsigned long long)blockIdx.y * 8 + ty; r < D.n_red; r += 8ull * gridDim.y) {
-            unsigned long long rem = r;
-            for (int k = (int)D.n_r - 1; k >= 0; k--) { const unsigned d = D.rd[k]; c[d] = (unsigned)(rem % D.dims[d]); rem /= D.dims[d]; }
+            decode_dims(r, D.rd, (int)D.n_r, D.dims, c);
             float res[1];
             eval_at<EV, 1>(D, c, res);
             acc = red_combine(rtype, acc, res[0]);
