@@ -1,0 +1,111 @@
+// backend/cuda/_.c — CUDA backend hub for TinyHVM: the `Backend cuda_backend`
+// vtable instance, bound at run time to libthvm_cuda.so.
+//
+// This is the reference-side half of the drop-in: it is written against the
+// reference's own header (src/tinyhvm.h:988-1046, struct Backend) and is meant
+// to sit beside src/backend/cpu/_.c and src/backend/metal/_.m.  A driver
+// includes it after "tinyhvm.c" exactly like the other hubs
+// (test/test_mm_dup_2arm.m:14-18):
+//
+//     #include "tinyhvm.c"
+//     #include "backend/cpu/_.c"
+//     #include "backend/cuda/_.c"
+//
+// The library is opened with dlopen on first init, so a build of this file
+// has no link-time CUDA dependency and a host without a GPU can still run the
+// CPU backend.  There is no silent fallback: if "cuda" is requested and the
+// library or a device is missing, thvm_init_device() aborts.
+//
+// Every slot is the like-named entry point of include/thvm_cuda.h; the PODs
+// (View, ShapeTracker, FusedOp, ReduceSpec, UOpKernel) cross the boundary by
+// pointer and are layout-identical (checked below).
+#ifndef THVM_BACKEND_CUDA_HUB
+#define THVM_BACKEND_CUDA_HUB
+
+#include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include "thvm_cuda.h"
+
+_Static_assert(sizeof(thc_shape_t) == sizeof(Shape), "Shape mirror");
+_Static_assert(sizeof(thc_view_t) == sizeof(View), "View mirror");
+_Static_assert(offsetof(thc_view_t, compound_masks) == offsetof(View, compound_masks), "View mirror");
+_Static_assert(sizeof(thc_tracker_t) == sizeof(ShapeTracker), "ShapeTracker mirror");
+_Static_assert(sizeof(thc_fused_op_t) == sizeof(FusedOp), "FusedOp mirror");
+_Static_assert(sizeof(thc_reduce_spec_t) == sizeof(ReduceSpec), "ReduceSpec mirror");
+_Static_assert(sizeof(thc_uop_kernel_t) == sizeof(UOpKernel), "UOpKernel mirror");
+
+#define THVM_DEV_CUDA 2   // backends[0] = cpu, [1] = metal (src/tinyhvm.h:1052-1054)
+
+Backend cuda_backend;     // filled by cuda_hub_init
+static void *cuda_hub_lib = NULL;
+
+static void *cuda_hub_sym(const char *name) {
+    void *p = dlsym(cuda_hub_lib, name);
+    if (!p) { fprintf(stderr, "TinyHVM cuda: %s missing from libthvm_cuda.so\n", name); exit(1); }
+    return p;
+}
+
+// Backend.init: open the library, bind all slots, run the library's init.
+static int cuda_hub_init(void) {
+    if (!cuda_hub_lib) {
+        const char *path = getenv("THVM_CUDA_LIB");
+        cuda_hub_lib = dlopen(path ? path : "libthvm_cuda.so", RTLD_NOW | RTLD_LOCAL);
+        if (!cuda_hub_lib) { fprintf(stderr, "TinyHVM cuda: %s\n", dlerror()); return 1; }
+        Backend *b = &cuda_backend;
+        b->shutdown            = cuda_hub_sym("thvm_cuda_shutdown");
+        b->buf_alloc           = cuda_hub_sym("thvm_cuda_buf_alloc");
+        b->buf_free            = cuda_hub_sym("thvm_cuda_buf_free");
+        b->buf_incref          = cuda_hub_sym("thvm_cuda_buf_incref");
+        b->buf_decref          = cuda_hub_sym("thvm_cuda_buf_decref");
+        b->mem_checkpoint      = cuda_hub_sym("thvm_cuda_mem_checkpoint");
+        b->buf_mark_use        = cuda_hub_sym("thvm_cuda_buf_mark_use");
+        b->buf_write           = cuda_hub_sym("thvm_cuda_buf_write");
+        b->buf_read            = cuda_hub_sym("thvm_cuda_buf_read");
+        b->op_unary            = cuda_hub_sym("thvm_cuda_op_unary");
+        b->op_binary           = cuda_hub_sym("thvm_cuda_op_binary");
+        b->op_mm               = cuda_hub_sym("thvm_cuda_op_mm");
+        b->op_reduce           = cuda_hub_sym("thvm_cuda_op_reduce");
+        b->dispatch_kernel_rs  = cuda_hub_sym("thvm_cuda_dispatch_kernel_rs");
+        // The scheduler prefers the lowered KOP form whenever this slot is set
+        // (src/schedule/_.c:2370).  The structured form carries the views and
+        // the reduce spec the kernel selection needs, so the slot stays NULL
+        // unless THVM_CUDA_UOP=1 asks for the KOP interpreter.
+        b->dispatch_uop_kernel = getenv("THVM_CUDA_UOP") ? cuda_hub_sym("thvm_cuda_dispatch_uop_kernel") : NULL;
+        b->contiguify          = cuda_hub_sym("thvm_cuda_contiguify");
+        b->buf_copy            = cuda_hub_sym("thvm_cuda_buf_copy");
+        b->buf_read_nosync     = cuda_hub_sym("thvm_cuda_buf_read_nosync");
+        b->adam_step           = cuda_hub_sym("thvm_cuda_adam_step");
+        b->pool_reset          = cuda_hub_sym("thvm_cuda_pool_reset");
+        b->pool_set_persistent = cuda_hub_sym("thvm_cuda_pool_set_persistent");
+        b->begin_batch         = cuda_hub_sym("thvm_cuda_begin_batch");
+        b->end_batch           = cuda_hub_sym("thvm_cuda_end_batch");
+        b->profile_report      = cuda_hub_sym("thvm_cuda_profile_report");
+        b->profile_reset       = cuda_hub_sym("thvm_cuda_profile_reset");
+    }
+    int (*lib_init)(void) = cuda_hub_sym("thvm_cuda_init");
+    return lib_init();
+}
+
+Backend cuda_backend = { .init = cuda_hub_init };
+
+// thvm_init with a "cuda" branch, mirroring the Metal branch of the
+// reference's thvm_init (src/ctx/init.c:24-35).  `base_init` is the reference's
+// own thvm_init (a driver that cannot edit src/ctx/init.c renames it with
+// `#define thvm_init thvm_init_base` around `#include "tinyhvm.c"`).
+static TinyHVM *thvm_init_device(TinyHVM *(*base_init)(const char *), const char *device) {
+    TinyHVM *ctx = base_init(device);
+    if (device && (strcmp(device, "cuda") == 0 || strcmp(device, "b200") == 0)) {
+        if (cuda_backend.init() != 0) {
+            fprintf(stderr, "TinyHVM: requested cuda backend unavailable (no CPU fallback)\n");
+            exit(1);
+        }
+        ctx->backends[THVM_DEV_CUDA] = &cuda_backend;
+        ctx->n_backends = THVM_DEV_CUDA + 1;
+        ctx->default_device = THVM_DEV_CUDA;
+    }
+    return ctx;
+}
+
+#endif  // THVM_BACKEND_CUDA_HUB

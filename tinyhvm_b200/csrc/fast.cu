@@ -87,7 +87,24 @@ struct StaticEval {
 // ------------------------------------------------------------------ leaf access
 // V consecutive elements along the innermost collapsed dim, starting at coords c.
 template <int V>
-__device__ __forceinline__ void load_leaf(const FLeaf &L, const unsigned *c, int rank, float (&dst)[V]) {
+__device__ __forceinline__ void load_leaf(const FLeaf &L, const unsigned *c, int rank, unsigned long long flat, float (&dst)[V]) {
+    if (L.mode == 2) {                       // a single element, broadcast
+        const float s = L.ptr[L.off];
+#pragma unroll
+        for (int k = 0; k < V; k++) dst[k] = s;
+        return;
+    }
+    if (L.mode == 1) {                       // laid out exactly like the iteration space
+        const float *p = L.ptr + (L.off + (long long)flat);
+        if (V == 4 && L.vec) {
+            const float4 q = *reinterpret_cast<const float4 *>(p);
+            dst[0] = q.x; dst[1] = q.y; dst[2] = q.z; dst[3] = q.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; k++) dst[k] = p[k];
+        }
+        return;
+    }
     long long off = L.off;
     bool dead = false;
 #pragma unroll
@@ -123,12 +140,12 @@ __device__ __forceinline__ void load_leaf(const FLeaf &L, const unsigned *c, int
 }
 
 template <class EV, int V>
-__device__ __forceinline__ void eval_at(const FDesc &D, const unsigned *c, float (&res)[V]) {
+__device__ __forceinline__ void eval_at(const FDesc &D, const unsigned *c, unsigned long long flat, float (&res)[V]) {
     float v[EV::NV][V];
     const int nl = EV::nleaves(D.prog);
 #pragma unroll
     for (int i = 0; i < EV::MAXL; i++)
-        if (i < nl) load_leaf<V>(D.leaf[i], c, (int)D.rank, v[i]);
+        if (i < nl) load_leaf<V>(D.leaf[i], c, (int)D.rank, flat, v[i]);
     EV::template run<V>(D.prog, v);
     const int r = EV::result(D.prog);
 #pragma unroll
@@ -171,10 +188,21 @@ __global__ void __launch_bounds__(256) k_ew(const __grid_constant__ FDesc D, flo
             c[0] = (unsigned)rem;
         }
         float res[V];
-        eval_at<EV, V>(D, c, res);
+        eval_at<EV, V>(D, c, flat, res);
         if (V == 4) *reinterpret_cast<float4 *>(out + flat) = make_float4(res[0], res[1], res[2], res[3]);
         else out[flat] = res[0];
     }
+}
+
+// coordinates (into c) and flat position of reduce index r for an output whose
+// kept coordinates are already in c and whose kept flat position is kflat
+__device__ __forceinline__ unsigned long long red_position(const FDesc &D, unsigned long long r, bool one_r,
+                                                           unsigned long long kflat, unsigned *c) {
+    if (one_r) { c[D.rd[0]] = (unsigned)r; return kflat + r * D.fstride[D.rd[0]]; }
+    decode_dims(r, D.rd, (int)D.n_r, D.dims, c);
+    unsigned long long f = kflat;
+    for (int k = 0; k < (int)D.n_r; k++) f += (unsigned long long)c[D.rd[k]] * D.fstride[D.rd[k]];
+    return f;
 }
 
 // ------------------------------------------------------------------ reduce, innermost dim reduced
@@ -194,6 +222,9 @@ __global__ void __launch_bounds__(256) k_red_inner(const __grid_constant__ FDesc
         const unsigned s = (unsigned)(gi % D.split);
         unsigned c[FR];
         decode_dims(o, D.kd, (int)D.n_k, D.dims, c);
+        unsigned long long kflat = 0;           // flat position of the kept coordinates
+        for (int k = 0; k < (int)D.n_k; k++) kflat += (unsigned long long)c[D.kd[k]] * D.fstride[D.kd[k]];
+        const bool one_r = D.n_r == 1;          // a single reduced dim: the innermost one, stride 1 in flat space
         const unsigned long long lo = (unsigned long long)s * chunk;
         const unsigned long long hi = lo + chunk < items ? lo + chunk : items;
         float acc = red_init(rtype);
@@ -206,20 +237,20 @@ __global__ void __launch_bounds__(256) k_red_inner(const __grid_constant__ FDesc
 #pragma unroll
             for (int d = 0; d < FR; d++) c2[d] = c[d];
             for (; it + G < hi; it += 2 * G) {
-                decode_dims(it * V, D.rd, (int)D.n_r, D.dims, c);
-                decode_dims((it + G) * V, D.rd, (int)D.n_r, D.dims, c2);
+                const unsigned long long f1 = red_position(D, it * V, one_r, kflat, c);
+                const unsigned long long f2 = red_position(D, (it + G) * V, one_r, kflat, c2);
                 float r1[V], r2[V];
-                eval_at<EV, V>(D, c, r1);
-                eval_at<EV, V>(D, c2, r2);
+                eval_at<EV, V>(D, c, f1, r1);
+                eval_at<EV, V>(D, c2, f2, r2);
 #pragma unroll
                 for (int k = 0; k < V; k++) { acc = red_combine(rtype, acc, r1[k]); acc2 = red_combine(rtype, acc2, r2[k]); }
             }
             acc = red_combine(rtype, acc, acc2);
         }
         for (; it < hi; it += G) {
-            decode_dims(it * V, D.rd, (int)D.n_r, D.dims, c);
+            const unsigned long long f1 = red_position(D, it * V, one_r, kflat, c);
             float res[V];
-            eval_at<EV, V>(D, c, res);
+            eval_at<EV, V>(D, c, f1, res);
 #pragma unroll
             for (int k = 0; k < V; k++) acc = red_combine(rtype, acc, res[k]);
         }
@@ -253,12 +284,14 @@ __global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc
     if (live) {
         decode_dims(o, D.kd, (int)D.n_k, D.dims, c);
     }
+    unsigned long long kflat = 0;
+    for (int k = 0; k < (int)D.n_k; k++) kflat += (unsigned long long)c[D.kd[k]] * D.fstride[D.kd[k]];
     float acc = red_init(rtype);
     if (live)
         for (unsigned long long r = (unsigned long long)blockIdx.y * 8 + ty; r < D.n_red; r += 8ull * gridDim.y) {
-            decode_dims(r, D.rd, (int)D.n_r, D.dims, c);
+            const unsigned long long f1 = red_position(D, r, D.n_r == 1, kflat, c);
             float res[1];
-            eval_at<EV, 1>(D, c, res);
+            eval_at<EV, 1>(D, c, f1, res);
             acc = red_combine(rtype, acc, res[0]);
         }
     part[ty][tx] = acc;
@@ -354,6 +387,10 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
         if (dims[d].red) { D.rd[D.n_r++] = d; D.n_red *= dims[d].n; } else { D.kd[D.n_k++] = d; D.n_out *= dims[d].n; }
     }
     const int in = nd - 1;
+    {
+        unsigned long long w = 1;
+        for (int d = nd - 1; d >= 0; d--) { D.fstride[d] = w; w *= D.dims[d]; }
+    }
     bool vec_ok = D.dims[in] % 4 == 0;
     for (unsigned i = 0; i < H.n_leaves; i++) {
         FLeaf &L = D.leaf[i];
@@ -373,6 +410,12 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
         if (!(cst[i][in] == 1 || cst[i][in] == 0)) lv = false;
         if (cst[i][in] == 1 && (L.off % 4) != 0) lv = false;
         L.vec = lv ? 1u : 0u;
+        bool flat = L.masked == 0, single = L.masked == 0;
+        for (int d = 0; d < nd; d++) {
+            if ((unsigned long long)cst[i][d] != D.fstride[d] || cst[i][d] < 0) flat = false;
+            if (cst[i][d] != 0) single = false;
+        }
+        L.mode = single ? 2u : (flat ? 1u : 0u);
     }
     D.vec = vec_ok ? 4u : 1u;
     D.split = 1;

@@ -19,6 +19,7 @@ struct FLeaf {
     unsigned     mlo[FR], mhi[FR];   // valid coordinate range [mlo, mhi) where masked
     unsigned     masked;         // bit d set: dim d carries a partial mask
     unsigned     vec;            // 1: 16-byte loads along the innermost dim are legal
+    unsigned     mode;           // 0: strided (general), 1: flat (off + row-major position), 2: one element
 };
 
 struct FProg {
@@ -37,6 +38,7 @@ struct FDesc {
     unsigned vec;                // elements per thread along the innermost dim (1 or 4)
     unsigned split;              // CTAs sharing one output (two-pass reduce), >= 1
     unsigned chain;              // index into the static chain registry, or 0 = interpreted
+    unsigned long long fstride[FR];  // row-major strides of the collapsed dims (flat position of a coordinate)
     FLeaf    leaf[FL];
     FProg    prog;
 };
