@@ -123,9 +123,10 @@ static Term ce_backward(TinyHVM *ctx, Term logits, const u8 *labels, u32 B, u32 
 
 /* y = x@W + b, realised, as [B,N] */
 static Term linear_fwd(TinyHVM *ctx, Term x, Term W, Term b, u32 B, u32 N) {
-    const Term bt = b;
-    (void)B; (void)N;
-    return realize(ctx, thvm_tg_linear(ctx, x, W, &bt));
+    /* same composition as thvm_tg_linear (src/nn/tg_tensor.c:34-88), which insists
+     * on a realised x; here x may be a lazy view of a realised tensor */
+    Term bc = thvm_expand(ctx, thvm_reshape(ctx, b, SHAPE(1, N)), SHAPE(B, N));
+    return realize(ctx, op2(ctx, UOP_ADD, thvm_mm(ctx, x, W), bc));
 }
 
 /* ------------------------------------------------------------------ config 1 */

@@ -1,1 +1,163 @@
-/* CNN drivers: filled in below */
+/* ref_host_cnn.c — staged CNN training steps (LeNet-5, VGG-style) written with
+ * the reference's own lazy-tensor API; included by ref_host.c.
+ *
+ * TEST INFRASTRUCTURE ONLY (see ref_host.c).  Every backward expression follows
+ * the rule body of the reference's autograd it stands in for:
+ *   RELU   da * CMP(a,0)                         src/interact/grad.c:194-202
+ *   MM     gy @ b^T,  a^T @ gy                   src/interact/grad.c:483-496
+ *   RMAX   da * (1 - CMP(expand(rmax(a)), a))    src/interact/grad.c:406-425 (ties all get the gradient)
+ *   EXPAND sum to the source shape               src/interact/grad.c:379-404
+ *   PAD <-> SHRINK                               src/interact/grad.c:317-373
+ * Staging rules: a realised TAG_TEN may be shared; every lazy view is rebuilt
+ * per consumer; padding is materialised (ADD(pad(x),0)) before a convolution;
+ * a permute is materialised before a rank-changing reshape.
+ */
+
+/* The reference's lowered CPU path loads before it masks and walks off the buffer
+ * on padded views (src/lower/_.c:303-307, src/backend/cpu/uop.c:55-69); its
+ * FusedOp interpreter handles them, so CPU runs of programs with padding use it. */
+static void cpu_masked_leaf_workaround(const char *dev) {
+    if (strcmp(dev, "cpu") == 0) setenv("THVM_NO_LOWER", "1", 1); else unsetenv("THVM_NO_LOWER");
+}
+
+static Term as4(TinyHVM *ctx, Term raw, u32 a, u32 b, u32 c, u32 d) { return thvm_reshape(ctx, raw, SHAPE(a, b, c, d)); }
+static Term sum023(TinyHVM *ctx, Term t) { return thvm_sum_axes(ctx, t, (u32[]){0, 2, 3}, 3); }
+
+/* zero padding of H and W by p, materialised */
+static Term pad_hw(TinyHVM *ctx, Term x, u32 p) {
+    if (!p) return x;
+    u32 pairs[8] = {0, 0, 0, 0, p, p, p, p};
+    return realize(ctx, op2(ctx, UOP_ADD, thvm_pad(ctx, x, pairs, 4), scalar(ctx, 0.f)));
+}
+
+/* conv (stride 1, input already padded) + optional bias; returns the realised pre-activation */
+static Term conv_fwd(TinyHVM *ctx, Term xp, Term W, Term bias) {
+    return realize(ctx, thvm_conv2d(ctx, xp, W, bias, 1, (u32[]){1, 1}, (u32[]){0, 0, 0, 0}));
+}
+
+/* dW[Co,Ci,K,K] = sum over B,OH,OW of window(xp) * g : a 7-D MUL + SUM{0,3,4}; raw result */
+static Term conv_wgrad(TinyHVM *ctx, Term xp, Term g4, u32 B, u32 Ci, u32 Co, u32 OH, u32 OW, u32 K) {
+    Term P = thvm_pool(ctx, xp, (u32[]){K, K}, (u32[]){1, 1}, 2);                       /* [B,Ci,OH,OW,K,K] */
+    Term xr = thvm_expand(ctx, thvm_reshape(ctx, P, SHAPE(B, 1, Ci, OH, OW, K, K)), SHAPE(B, Co, Ci, OH, OW, K, K));
+    Term gr = thvm_expand(ctx, thvm_reshape(ctx, g4, SHAPE(B, Co, 1, OH, OW, 1, 1)), SHAPE(B, Co, Ci, OH, OW, K, K));
+    return realize(ctx, thvm_sum_axes(ctx, op2(ctx, UOP_MUL, xr, gr), (u32[]){0, 3, 4}, 3));
+}
+
+/* gradient w.r.t. the (padded) conv input: full correlation of the K-1 padded
+ * upstream gradient with the spatially flipped, channel-transposed weight.  The
+ * flip is not expressible as a view (the lowerer rejects negative strides,
+ * src/lower/_.c:452-455), so the weight goes through the host, identically for
+ * every backend.  Raw result, logical shape [B,Ci,OH+K-1,OW+K-1]. */
+static Term conv_dgrad(TinyHVM *ctx, Term g4, Term W, u32 Ci, u32 Co, u32 K) {
+    f32 *hw = thvm_to_host(ctx, W);
+    f32 *wf = malloc((size_t)Co * Ci * K * K * 4);
+    for (u32 o = 0; o < Co; o++) for (u32 c = 0; c < Ci; c++) for (u32 p = 0; p < K; p++) for (u32 q = 0; q < K; q++)
+        wf[((c * Co + o) * K + (K - 1 - p)) * K + (K - 1 - q)] = hw[((o * Ci + c) * K + p) * K + q];
+    Term tWf = thvm_tensor(ctx, wf, SHAPE(Ci, Co, K, K));
+    free(wf);
+    Term gp = pad_hw(ctx, g4, K - 1);
+    return realize(ctx, thvm_conv2d(ctx, gp, tWf, term_era(), 1, (u32[]){1, 1}, (u32[]){0, 0, 0, 0}));
+}
+
+/* 2x2/2 max-pool forward; raw result [B,C,OH,OW,1,1] */
+static Term pool_fwd(TinyHVM *ctx, Term a4) { return realize(ctx, thvm_maxpool2d(ctx, a4, (u32[]){2, 2}, (u32[]){2, 2})); }
+
+static Term pool_window(TinyHVM *ctx, Term a4, u32 B, u32 C, u32 OH, u32 OW) {
+    return thvm_permute(ctx, thvm_reshape(ctx, a4, SHAPE(B, C, OH, 2, OW, 2)), (u32[]){0, 1, 2, 4, 3, 5}, 6);
+}
+
+/* max-pool backward, mask form; returns a realised contiguous [B,C,OH,2,OW,2] buffer (= [B,C,H,W]) */
+static Term pool_bwd(TinyHVM *ctx, Term a4, Term m_raw, Term g_raw, u32 B, u32 C, u32 OH, u32 OW) {
+    Term m6 = thvm_expand(ctx, thvm_reshape(ctx, m_raw, SHAPE(B, C, OH, OW, 1, 1)), SHAPE(B, C, OH, OW, 2, 2));
+    Term mask = op2(ctx, UOP_SUB, scalar(ctx, 1.f), op2(ctx, UOP_CMP, m6, pool_window(ctx, a4, B, C, OH, OW)));
+    Term g6 = thvm_expand(ctx, thvm_reshape(ctx, g_raw, SHAPE(B, C, OH, OW, 1, 1)), SHAPE(B, C, OH, OW, 2, 2));
+    Term dwin = realize(ctx, op2(ctx, UOP_MUL, g6, mask));
+    return realize(ctx, op2(ctx, UOP_ADD, thvm_permute(ctx, dwin, (u32[]){0, 1, 2, 4, 3, 5}, 6), scalar(ctx, 0.f)));
+}
+
+/* relu backward: g * (u > 0), realised */
+static Term relu_bwd(TinyHVM *ctx, Term g, Term u) { return realize(ctx, op2(ctx, UOP_MUL, g, op2(ctx, UOP_CMP, u, scalar(ctx, 0.f)))); }
+
+/* SGD write-back: w <- w - lr * g  (ASSIGN rule, src/interact/tensor_ops.c:3-160) */
+static void sgd(TinyHVM *ctx, Term w, Term g_view, f32 lr) {
+    thvm_eval(ctx, thvm_assign(ctx, w, op2(ctx, UOP_SUB, w, op2(ctx, UOP_MUL, g_view, scalar(ctx, lr)))));
+}
+
+static void keepf(TinyHVM *ctx, const char *fmt, u32 step, Term t) { char nm[64]; snprintf(nm, sizeof nm, fmt, step); keep(ctx, nm, t); }
+
+/* ------------------------------------------------------------------ config 4: LeNet-5 */
+/* params (flat, in this order): W1[6,1,5,5] b1[6] W2[16,6,5,5] b2[16] W3[400,120] b3[120] W4[120,84] b4[84] W5[84,10] b5[10]
+ * x[steps][B,1,28,28], labels[steps][B].  Keeps the loss of every step, the
+ * gradients of step 0 and the parameters after the last step. */
+int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 keep_grads) {
+    cpu_masked_leaf_workaround(dev);
+    TinyHVM *ctx = thvm_init(dev);
+    const f32 *p = params;
+    Term W1 = thvm_tensor(ctx, p, SHAPE(6, 1, 5, 5)); p += 150;   Term b1 = thvm_tensor(ctx, p, SHAPE(6)); p += 6;
+    Term W2 = thvm_tensor(ctx, p, SHAPE(16, 6, 5, 5)); p += 2400; Term b2 = thvm_tensor(ctx, p, SHAPE(16)); p += 16;
+    Term W3 = thvm_tensor(ctx, p, SHAPE(400, 120)); p += 48000;   Term b3 = thvm_tensor(ctx, p, SHAPE(120)); p += 120;
+    Term W4 = thvm_tensor(ctx, p, SHAPE(120, 84)); p += 10080;    Term b4 = thvm_tensor(ctx, p, SHAPE(84)); p += 84;
+    Term W5 = thvm_tensor(ctx, p, SHAPE(84, 10)); p += 840;       Term b5 = thvm_tensor(ctx, p, SHAPE(10)); p += 10;
+    u32 keep_id = ctx->tensor_count;
+    double t0 = now_s();
+    for (u32 s = 0; s < steps; s++) {
+        Term tx = thvm_tensor(ctx, x + (size_t)s * B * 784, SHAPE(B, 1, 28, 28));
+        const u8 *lab = labels + (size_t)s * B;
+        /* forward */
+        Term xp = pad_hw(ctx, tx, 2);                                        /* [B,1,32,32] */
+        Term u1 = conv_fwd(ctx, xp, W1, b1);                                 /* [B,6,28,28] */
+        Term a1 = realize(ctx, op1(ctx, UOP_RELU, u1));
+        Term p1 = pool_fwd(ctx, a1);                                         /* raw [B,6,14,14,1,1] */
+        Term u2 = conv_fwd(ctx, as4(ctx, p1, B, 6, 14, 14), W2, b2);         /* [B,16,10,10] */
+        Term a2 = realize(ctx, op1(ctx, UOP_RELU, u2));
+        Term p2 = pool_fwd(ctx, a2);                                         /* raw [B,16,5,5,1,1] */
+        Term u3 = linear_fwd(ctx, as2(ctx, p2, B, 400), W3, b3, B, 120);
+        Term a3 = realize(ctx, op1(ctx, UOP_RELU, u3));
+        Term u4 = linear_fwd(ctx, a3, W4, b4, B, 84);
+        Term a4 = realize(ctx, op1(ctx, UOP_RELU, u4));
+        Term logits = linear_fwd(ctx, a4, W5, b5, B, 10);
+        Term loss = realize(ctx, cross_entropy_loss(ctx, logits, (u8 *)lab, B, 10));
+        /* backward */
+        Term dl = ce_backward(ctx, logits, lab, B, 10);
+        Term dW5 = mm_raw(ctx, transpose2(ctx, a4), dl);
+        Term db5 = realize(ctx, thvm_sum_axes(ctx, dl, (u32[]){0}, 1));
+        Term da4 = mm_raw(ctx, dl, transpose2(ctx, W5));
+        Term du4 = relu_bwd(ctx, as2(ctx, da4, B, 84), u4);
+        Term dW4 = mm_raw(ctx, transpose2(ctx, a3), du4);
+        Term db4 = realize(ctx, thvm_sum_axes(ctx, du4, (u32[]){0}, 1));
+        Term da3 = mm_raw(ctx, du4, transpose2(ctx, W4));
+        Term du3 = relu_bwd(ctx, as2(ctx, da3, B, 120), u3);
+        Term dW3 = mm_raw(ctx, transpose2(ctx, as2(ctx, p2, B, 400)), du3);
+        Term db3 = realize(ctx, thvm_sum_axes(ctx, du3, (u32[]){0}, 1));
+        Term dp2 = mm_raw(ctx, du3, transpose2(ctx, W3));                    /* raw [B,1,400] */
+        Term da2 = pool_bwd(ctx, a2, p2, dp2, B, 16, 5, 5);                  /* [B,16,10,10] */
+        Term du2 = relu_bwd(ctx, as4(ctx, da2, B, 16, 10, 10), u2);
+        Term dW2 = conv_wgrad(ctx, as4(ctx, p1, B, 6, 14, 14), du2, B, 6, 16, 10, 10, 5);
+        Term db2 = realize(ctx, sum023(ctx, du2));
+        Term dp1 = conv_dgrad(ctx, du2, W2, 6, 16, 5);                       /* raw [B,6,14,14] */
+        Term da1 = pool_bwd(ctx, a1, p1, dp1, B, 6, 14, 14);                 /* [B,6,28,28] */
+        Term du1 = relu_bwd(ctx, as4(ctx, da1, B, 6, 28, 28), u1);
+        Term dW1 = conv_wgrad(ctx, xp, du1, B, 1, 6, 28, 28, 5);
+        Term db1 = realize(ctx, sum023(ctx, du1));
+        keepf(ctx, "loss%u", s, loss);
+        if (s == 0 && keep_grads) {
+            keep(ctx, "logits", logits);
+            keep(ctx, "dW1", dW1); keep(ctx, "db1", db1); keep(ctx, "dW2", dW2); keep(ctx, "db2", db2);
+            keep(ctx, "dW3", dW3); keep(ctx, "db3", db3); keep(ctx, "dW4", dW4); keep(ctx, "db4", db4);
+            keep(ctx, "dW5", dW5); keep(ctx, "db5", db5);
+        }
+        /* update */
+        sgd(ctx, W1, as4(ctx, dW1, 6, 1, 5, 5), lr);   sgd(ctx, b1, as1(ctx, db1, 6), lr);
+        sgd(ctx, W2, as4(ctx, dW2, 16, 6, 5, 5), lr);  sgd(ctx, b2, as1(ctx, db2, 16), lr);
+        sgd(ctx, W3, as2(ctx, dW3, 400, 120), lr);     sgd(ctx, b3, as1(ctx, db3, 120), lr);
+        sgd(ctx, W4, as2(ctx, dW4, 120, 84), lr);      sgd(ctx, b4, as1(ctx, db4, 84), lr);
+        sgd(ctx, W5, as2(ctx, dW5, 84, 10), lr);       sgd(ctx, b5, as1(ctx, db5, 10), lr);
+        f32 *sync = thvm_to_host(ctx, b5); (void)sync;                       /* drain the device queue before the clock stops */
+        if (s + 1 < steps) { thvm_reset(ctx, keep_id); thvm_sched_reset_runtime(); }
+    }
+    drv_secs = now_s() - t0;
+    keep(ctx, "W1", W1); keep(ctx, "b1", b1); keep(ctx, "W2", W2); keep(ctx, "b2", b2); keep(ctx, "W3", W3);
+    keep(ctx, "b3", b3); keep(ctx, "W4", W4); keep(ctx, "b4", b4); keep(ctx, "W5", W5); keep(ctx, "b5", b5);
+    thvm_free(ctx);
+    return 0;
+}
