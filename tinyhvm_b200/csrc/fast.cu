@@ -446,7 +446,9 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
     if (D.is_red[in]) {
         F.strategy = 1;
         const unsigned long long items = D.n_red / D.vec;
-        F.group = items >= 1024 ? 256 : (items >= 32 ? 32 : 1);
+        // A warp per output needs no block barrier; a CTA per output only pays off
+        // when there are too few outputs for warps alone to keep HBM busy.
+        F.group = items < 32 ? 1 : ((items < 1024 || D.n_out >= 16ull * sms) ? 32 : 256);
         if (F.group == 256 && D.n_out < 2ull * sms) {
             unsigned long long want = (4ull * sms + D.n_out - 1) / D.n_out;
             unsigned long long most = items / 1024;                 // keep >= 4 vectors per thread per slice
@@ -470,11 +472,12 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
 }
 
 void classify_plan(Plan *p) {
+    if (try_contraction(p)) return;
     FastDesc *F = new FastDesc();
     if (build_fast(p->host, *F)) { p->fast = (struct FastDesc *)F; p->kind = F->strategy == 0 ? PLAN_EW : PLAN_REDUCE; }
     else { delete F; p->fast = nullptr; p->kind = PLAN_GENERIC; }
 }
-void free_fast(Plan *p) { delete (FastDesc *)p->fast; p->fast = nullptr; }
+void free_fast(Plan *p) { delete (FastDesc *)p->fast; p->fast = nullptr; free_contraction(p); }
 
 // ------------------------------------------------------------------ host: launch
 template <class EV>
@@ -510,6 +513,7 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
 }
 
 bool launch_fast(Plan *p, const GenArgs &args) {
+    if (p->kind == PLAN_CONTRACT) return launch_contraction(p, args);
     FastDesc &F = *(FastDesc *)p->fast;
     FDesc D = F.d;
     for (unsigned i = 0; i < D.prog.n_leaves; i++) {

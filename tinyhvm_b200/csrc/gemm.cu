@@ -1,0 +1,278 @@
+// gemm.cu — contraction kernel on the 5th-generation tensor cores (tcgen05,
+// accumulators in tensor memory) with a 3xTF32 operand split that keeps f32
+// accuracy: x = hi + lo with hi = tf32(x), lo = tf32(x - hi), and
+//     a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi        (f32 accumulate in TMEM).
+//
+// It serves every SUM(MUL(a,b)) dispatch whose operands are separable
+// (gemm_desc.h): matmul in all four transpose forms, and convolution forward /
+// weight gradient / input gradient, which the reference expresses as MUL + SUM
+// over expanded pool views (src/ctx/init.c:555-582, src/nn/conv.c:390-478) and
+// its CPU backend evaluates one product at a time (src/backend/cpu/dispatch.c:169-218).
+//
+// One CTA computes one 128x128 tile of C.  Warps 0-7 are producers: they gather
+// the 128x32 A and B k-blocks from global memory through the separable offsets
+// (implicit im2col: no expanded copy of the input ever exists), split each value
+// and store hi and lo tiles into shared memory in the K-major 128-byte-swizzled
+// layout the MMA reads; two groups of four warps alternate k-blocks so one
+// group's global loads overlap the other's stores.  Warp 8 issues the MMAs (one
+// elected lane): per k-block 4 k-steps x 3 products, then tcgen05.commit hands
+// the stage back.  After the last k-block all eight producer warps read the
+// accumulators back with tcgen05.ld and store C through its separable offsets.
+// Stages are guarded by mbarriers; every wait is bounded and raises a status
+// bit instead of hanging.
+#include <string.h>
+#include <vector>
+#include "device_common.cuh"
+#include "gemm_desc.h"
+#include "plans.h"
+#include "state.h"
+
+namespace thc {
+
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int TILE_BYTES = 128 * BK * 4;            // one 128 x 32 f32 tile
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;         // A_hi, A_lo, B_hi, B_lo
+constexpr int GEMM_THREADS = 288;                   // 8 producer warps + 1 MMA warp
+constexpr int MMA_WARP = 8;
+constexpr int TMEM_COLS = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+enum : int { ERR_GEMM_TIMEOUT = 8 };
+
+struct GemmShared {                                 // follows the tile area in dynamic shared memory
+    long long am[BM], bn[BN], cm[BM], cn[BN];
+    unsigned long long full[STAGES], empty[STAGES], accum;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + sizeof(GemmShared) + 1024;   // + alignment slack
+
+// ---- PTX wrappers ----
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// bounded wait: false after WAIT_LIMIT polls or when another thread gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ uint32_t to_tf32(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return u; }
+// low part of the split; zero when the high part already is inf/nan (inf - inf would poison it)
+__device__ __forceinline__ uint32_t tf32_rest(float x, uint32_t hi) {
+    return (hi & 0x7F800000u) == 0x7F800000u ? 0u : to_tf32(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor: D f32, A/B tf32, both K-major, N = 128, M = 128
+constexpr uint32_t UMMA_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// mixed-radix decode of an index into its A/B and C element offsets
+__device__ __forceinline__ void decode_group(const GSub *subs, uint32_t n, uint32_t idx, bool use_b, long long &op, long long &oc) {
+    op = 0; oc = 0;
+    for (int i = (int)n - 1; i >= 0; i--) {
+        const uint32_t sz = subs[i].size, q = idx / sz, c = idx - q * sz;
+        op += (long long)c * (use_b ? subs[i].sb : subs[i].sa);
+        oc += (long long)c * subs[i].sc;
+        idx = q;
+    }
+}
+
+// one operand k-block: gather 8 (row, 16-byte chunk) units per thread
+__device__ __forceinline__ void gather_units(const float *__restrict__ P, long long base, const long long *rowoff,
+                                             const int32_t *__restrict__ ktab, uint32_t rows_valid, uint32_t k0, uint32_t K,
+                                             uint32_t kfast, uint32_t kvec, uint32_t t, float4 (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t row = kfast ? (t >> 3) + 16u * i : t;
+        const uint32_t chunk = kfast ? (t & 7u) : (uint32_t)i;
+        const uint32_t k = k0 + 4u * chunk;
+        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < rows_valid && k < K) {
+            const float *p = P + base + rowoff[row];
+            if (kvec) r = *reinterpret_cast<const float4 *>(p + ktab[k]);
+            else {
+                r.x = p[ktab[k]];
+                if (k + 1 < K) r.y = p[ktab[k + 1]];
+                if (k + 2 < K) r.z = p[ktab[k + 2]];
+                if (k + 3 < K) r.w = p[ktab[k + 3]];
+            }
+        }
+        v[i] = r;
+    }
+}
+// split and store the 8 units into the hi and lo tiles (K-major, 128-byte swizzle)
+__device__ __forceinline__ void store_units(uint32_t hi_tile, uint32_t lo_tile, uint32_t kfast, uint32_t t, const float4 (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t row = kfast ? (t >> 3) + 16u * i : t;
+        const uint32_t chunk = kfast ? (t & 7u) : (uint32_t)i;
+        const uint32_t off = (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+        const uint32_t h0 = to_tf32(v[i].x), h1 = to_tf32(v[i].y), h2 = to_tf32(v[i].z), h3 = to_tf32(v[i].w);
+        st_shared_v4(hi_tile + off, h0, h1, h2, h3);
+        st_shared_v4(lo_tile + off, tf32_rest(v[i].x, h0), tf32_rest(v[i].y, h1), tf32_rest(v[i].z, h2), tf32_rest(v[i].w, h3));
+    }
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_constant__ GemmDesc G) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    GemmShared &S = *reinterpret_cast<GemmShared *>(tiles + (size_t)STAGES * STAGE_BYTES);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const uint32_t nkb_all = (G.K + BK - 1) / BK;
+    const uint32_t kb_lo = blockIdx.z * G.kb_chunk;                       // this CTA's share of the k-blocks (split-K)
+    const uint32_t nkb = nkb_all - kb_lo < G.kb_chunk ? nkb_all - kb_lo : G.kb_chunk;
+    volatile int *abort_flag = &S.abort_flag;
+
+    // ---- setup: barriers, tensor memory, row / column offsets of this tile ----
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&S.full[s]), 128); mbar_init(smem_u32(&S.empty[s]), 1); }
+        mbar_init(smem_u32(&S.accum), 1);
+        S.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid < BM) {
+        long long oa = 0, oc = 0;
+        if (m0 + tid < G.M) decode_group(G.md, G.nm, m0 + tid, false, oa, oc);
+        if (G.partial) oc = ((long long)blockIdx.z * G.M + (m0 + tid)) * G.N;      // dense partial tile
+        S.am[tid] = oa; S.cm[tid] = oc;
+    } else if (tid < BM + BN) {
+        const uint32_t j = tid - BM;
+        long long ob = 0, oc = 0;
+        if (n0 + j < G.N) decode_group(G.nd, G.nn, n0 + j, true, ob, oc);
+        if (G.partial) oc = n0 + j;
+        S.bn[j] = ob; S.cn[j] = oc;
+    }
+    float *const Cout = G.partial ? G.partial : G.C;
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = S.tmem_base;
+    const uint32_t tiles_s = smem_u32(tiles);
+    const uint32_t rows_a = G.M - m0 < (uint32_t)BM ? G.M - m0 : (uint32_t)BM;
+    const uint32_t rows_b = G.N - n0 < (uint32_t)BN ? G.N - n0 : (uint32_t)BN;
+
+    if (warp < MMA_WARP) {
+        // ================= producers =================
+        const uint32_t grp = warp >> 2, t = tid & 127u;
+        bool ok = true;
+        for (uint32_t kb = grp; kb < nkb && ok; kb += 2) {
+            const uint32_t s = kb % STAGES, use = kb / STAGES;
+            float4 va[8], vb[8];
+            gather_units(G.A, G.a_off, S.am, G.ka, rows_a, (kb_lo + kb) * BK, G.K, G.a_kfast, G.a_kvec, t, va);
+            gather_units(G.B, G.b_off, S.bn, G.kb, rows_b, (kb_lo + kb) * BK, G.K, G.b_kfast, G.b_kvec, t, vb);
+            if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[s]), (use - 1) & 1u, abort_flag);
+            if (!ok) break;
+            const uint32_t st = tiles_s + s * STAGE_BYTES;
+            store_units(st, st + TILE_BYTES, G.a_kfast, t, va);
+            store_units(st + 2 * TILE_BYTES, st + 3 * TILE_BYTES, G.b_kfast, t, vb);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the MMA
+            mbar_arrive(smem_u32(&S.full[s]));
+        }
+        // ================= epilogue =================
+        if (ok) ok = mbar_wait(smem_u32(&S.accum), 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);                                 // tcgen05.ld needs the whole warp
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const uint32_t q = warp & 3u, half = warp >> 2;
+            const uint32_t row = q * 32u + lane;
+            const bool row_ok = row < rows_a;
+            const long long crow = S.cm[row];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const uint32_t col0 = half * 64u + (uint32_t)c * 32u;
+                uint32_t r[32];
+                const uint32_t taddr = tmem + ((q * 32u) << 16) + col0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+                    if (G.c_nvec && col0 + 32u <= rows_b) {
+                        float4 *dst = reinterpret_cast<float4 *>(Cout + crow + S.cn[col0]);
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < rows_b) Cout[crow + S.cn[col0 + j]] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+        }
+    } else {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                const uint32_t s = kb % STAGES, use = kb / STAGES;
+                ok = mbar_wait(smem_u32(&S.full[s]), use & 1u, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = tiles_s + s * STAGE_BYTES;
+                const uint64_t a_hi = umma_desc(st), a_lo = umma_desc(st + TILE_BYTES);
+                const uint64_t b_hi = umma_desc(st + 2 * TILE_BYTES), b_lo = umma_desc(st + 3 * TILE_BYTES);
+#pragma unroll
+                for (uint32_t ks = 0; ks < BK / 8; ks++) {
+                    const uint64_t adv = (uint64_t)(ks * 2u);           // 8 tf32 = 32 bytes, in 16-byte units
+                    umma_tf32(tmem, a_lo + adv, b_hi + adv, UMMA_IDESC, (kb | ks) ? 1u : 0u);
+                    umma_tf32(tmem, a_hi + adv, b_lo + adv, UMMA_IDESC, 1u);
+                    umma_tf32(tmem, a_hi + adv, b_hi + adv, UMMA_IDESC, 1u);
+                }
+                umma_commit(smem_u32(&S.empty[s]));                      // stage free once these MMAs retire
+            }
+            if (ok) umma_commit(smem_u32(&S.accum));
+        }
+        __syncwarp();
+    }
+
+    // ---- teardown ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && S.abort_flag) atomicOr(G.status, ERR_GEMM_TIMEOUT);
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace thc
+
+#include "gemm_host.inc"

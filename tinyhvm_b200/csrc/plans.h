@@ -21,6 +21,7 @@ struct Plan {
     DTracker  *dev_trackers = nullptr;
     uint32_t   n_trackers = 0;
     FastDesc  *fast = nullptr;          // owned; null for PLAN_GENERIC
+    void      *contract = nullptr;      // owned (gemm.cu); set for PLAN_CONTRACT
 };
 
 // Decide the family for a freshly built plan (sets kind / fast).
@@ -28,5 +29,9 @@ void classify_plan(Plan *p);
 // Launch a non-generic plan; false means "could not, use the generic kernel".
 bool launch_fast(Plan *p, const GenArgs &args);
 void free_fast(Plan *p);
+// SUM(MUL(a,b)) with separable operands -> tensor-core contraction (gemm.cu)
+bool try_contraction(Plan *p);
+bool launch_contraction(Plan *p, const GenArgs &args);
+void free_contraction(Plan *p);
 
 }  // namespace thc
