@@ -24,7 +24,7 @@ FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wno-unuse
 
 
 def _newest_header() -> float:
-    hs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "thvm_cuda.h"]
+    hs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + [PKG.parent / "include" / "thvm_cuda.h"]
     return max(h.stat().st_mtime for h in hs)
 
 

@@ -35,6 +35,7 @@ constexpr int STAGE_BYTES = 4 * TILE_BYTES;         // A_hi, A_lo, B_hi, B_lo
 constexpr int GEMM_THREADS = 288;                   // 8 producer warps + 1 MMA warp
 constexpr int MMA_WARP = 8;
 constexpr int TMEM_COLS = 128;
+constexpr int LOOKAHEAD = 2;                        // k-blocks of cp.async in flight ahead of the split pass
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 enum : int { ERR_GEMM_TIMEOUT = 8 };
 
@@ -70,9 +71,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 __device__ __forceinline__ uint32_t to_tf32(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return u; }
-// low part of the split; zero when the high part already is inf/nan (inf - inf would poison it)
-__device__ __forceinline__ uint32_t tf32_rest(float x, uint32_t hi) {
-    return (hi & 0x7F800000u) == 0x7F800000u ? 0u : to_tf32(x - __uint_as_float(hi));
+// x = hi + lo with hi = x truncated to tf32 (what the MMA sees of the raw f32); lo is
+// exact in f32 and zero when x is inf/nan (inf - inf would poison the sum)
+__device__ __forceinline__ uint32_t tf32_low(uint32_t xbits) {
+    const uint32_t hi = xbits & 0xFFFFE000u;
+    return (hi & 0x7F800000u) == 0x7F800000u ? 0u : __float_as_uint(__uint_as_float(xbits) - __uint_as_float(hi));
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -103,39 +106,75 @@ __device__ __forceinline__ void decode_group(const GSub *subs, uint32_t n, uint3
     }
 }
 
-// one operand k-block: gather 8 (row, 16-byte chunk) units per thread
-__device__ __forceinline__ void gather_units(const float *__restrict__ P, long long base, const long long *rowoff,
-                                             const int32_t *__restrict__ ktab, uint32_t rows_valid, uint32_t k0, uint32_t K,
-                                             uint32_t kfast, uint32_t kvec, uint32_t t, float4 (&v)[8]) {
+// ---- producers: cp.async gather into the swizzled tile, then the low-part pass ----
+// Thread t of the 256 producers owns 4 (row, 16-byte chunk) units of each 128x32
+// operand tile: along k when k is the operand's contiguous direction (a warp
+// covers 4 rows x 128 bytes), else along the rows (a warp covers 32 rows of one
+// chunk, element-wise 4-byte copies that coalesce across lanes).
+__device__ __forceinline__ void unit_of(uint32_t kfast, uint32_t t, int i, uint32_t &row, uint32_t &chunk) {
+    if (kfast) { row = (t >> 3) + 32u * (uint32_t)i; chunk = t & 7u; }
+    else       { row = t & 127u; chunk = (t >> 7) + 2u * (uint32_t)i; }
+}
+__device__ __forceinline__ uint32_t unit_offset(uint32_t row, uint32_t chunk) {
+    return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// what a producer thread needs per operand, fixed for the whole tile: the global row
+// pointers, the column (k) offsets and the swizzled tile offsets of its 4 units
+struct UnitSet {
+    const float *rowptr[4];
+    uint32_t kcol[4], soff[4], live;       // live: bit i set when unit i's row is inside the matrix
+};
+__device__ __forceinline__ void make_units(UnitSet &U, const float *P, long long base, const long long *rowoff,
+                                           uint32_t rows_valid, uint32_t kfast, uint32_t t) {
+    U.live = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const uint32_t row = kfast ? (t >> 3) + 16u * i : t;
-        const uint32_t chunk = kfast ? (t & 7u) : (uint32_t)i;
-        const uint32_t k = k0 + 4u * chunk;
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row < rows_valid && k < K) {
-            const float *p = P + base + rowoff[row];
-            if (kvec) r = *reinterpret_cast<const float4 *>(p + ktab[k]);
-            else {
-                r.x = p[ktab[k]];
-                if (k + 1 < K) r.y = p[ktab[k + 1]];
-                if (k + 2 < K) r.z = p[ktab[k + 2]];
-                if (k + 3 < K) r.w = p[ktab[k + 3]];
-            }
-        }
-        v[i] = r;
+    for (int i = 0; i < 4; i++) {
+        uint32_t row, chunk;
+        unit_of(kfast, t, i, row, chunk);
+        const bool ok = row < rows_valid;
+        U.rowptr[i] = ok ? P + base + rowoff[row] : P;
+        U.kcol[i] = 4u * chunk;
+        U.soff[i] = unit_offset(row, chunk);
+        if (ok) U.live |= 1u << i;
     }
 }
-// split and store the 8 units into the hi and lo tiles (K-major, 128-byte swizzle)
-__device__ __forceinline__ void store_units(uint32_t hi_tile, uint32_t lo_tile, uint32_t kfast, uint32_t t, const float4 (&v)[8]) {
+// issue the asynchronous copies of one operand k-block into its raw (= high part) tile;
+// rows past the matrix edge and k past K are zero-filled (source size 0).  `klin` != 0:
+// the operand's k offset is k * klin (a single reduced dim), else it comes from `ktab`.
+__device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, const int32_t *__restrict__ ktab, long long klin,
+                                           uint32_t k0, uint32_t K, uint32_t kvec, uint32_t tile) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const uint32_t row = kfast ? (t >> 3) + 16u * i : t;
-        const uint32_t chunk = kfast ? (t & 7u) : (uint32_t)i;
-        const uint32_t off = (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
-        const uint32_t h0 = to_tf32(v[i].x), h1 = to_tf32(v[i].y), h2 = to_tf32(v[i].z), h3 = to_tf32(v[i].w);
-        st_shared_v4(hi_tile + off, h0, h1, h2, h3);
-        st_shared_v4(lo_tile + off, tf32_rest(v[i].x, h0), tf32_rest(v[i].y, h1), tf32_rest(v[i].z, h2), tf32_rest(v[i].w, h3));
+    for (int i = 0; i < 4; i++) {
+        const uint32_t k = k0 + U.kcol[i], dst = tile + U.soff[i];
+        const bool row_ok = (U.live >> i) & 1u;
+        if (kvec) {
+            const bool in = row_ok && k < K;
+            const long long ko = klin ? (long long)k * klin : (long long)(in ? ktab[k] : 0);
+            cp_async16(dst, in ? U.rowptr[i] + ko : P, in ? 16u : 0u);
+        } else {
+#pragma unroll
+            for (uint32_t e = 0; e < 4; e++) {
+                const bool in = row_ok && k + e < K;
+                const long long ko = klin ? (long long)(k + e) * klin : (long long)(in ? ktab[k + e] : 0);
+                cp_async4(dst + 4u * e, in ? U.rowptr[i] + ko : P, in ? 4u : 0u);
+            }
+        }
+    }
+}
+// low-part pass over this thread's own units: lo = x - trunc_tf32(x).  The raw f32
+// tile doubles as the high part: the tf32 MMA reads only the upper 19 bits.
+__device__ __forceinline__ void split_tile(const UnitSet &U, uint32_t raw_tile, uint32_t lo_tile) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t x0, x1, x2, x3;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(raw_tile + U.soff[i]) : "memory");
+        st_shared_v4(lo_tile + U.soff[i], tf32_low(x0), tf32_low(x1), tf32_low(x2), tf32_low(x3));
     }
 }
 
@@ -152,7 +191,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
 
     // ---- setup: barriers, tensor memory, row / column offsets of this tile ----
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&S.full[s]), 128); mbar_init(smem_u32(&S.empty[s]), 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&S.full[s]), 256); mbar_init(smem_u32(&S.empty[s]), 1); }
         mbar_init(smem_u32(&S.accum), 1);
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -184,21 +223,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
 
     if (warp < MMA_WARP) {
         // ================= producers =================
-        const uint32_t grp = warp >> 2, t = tid & 127u;
+        const uint32_t t = tid;                                          // 0..255
         bool ok = true;
-        for (uint32_t kb = grp; kb < nkb && ok; kb += 2) {
-            const uint32_t s = kb % STAGES, use = kb / STAGES;
-            float4 va[8], vb[8];
-            gather_units(G.A, G.a_off, S.am, G.ka, rows_a, (kb_lo + kb) * BK, G.K, G.a_kfast, G.a_kvec, t, va);
-            gather_units(G.B, G.b_off, S.bn, G.kb, rows_b, (kb_lo + kb) * BK, G.K, G.b_kfast, G.b_kvec, t, vb);
-            if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[s]), (use - 1) & 1u, abort_flag);
-            if (!ok) break;
-            const uint32_t st = tiles_s + s * STAGE_BYTES;
-            store_units(st, st + TILE_BYTES, G.a_kfast, t, va);
-            store_units(st + 2 * TILE_BYTES, st + 3 * TILE_BYTES, G.b_kfast, t, vb);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the MMA
-            mbar_arrive(smem_u32(&S.full[s]));
+        UnitSet UA, UB;
+        make_units(UA, G.A, G.a_off, S.am, rows_a, G.a_kfast, t);
+        make_units(UB, G.B, G.b_off, S.bn, rows_b, G.b_kfast, t);
+        auto issue = [&](uint32_t kb) {                                  // copies for local k-block kb into its stage
+            const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, k0 = (kb_lo + kb) * BK;
+            issue_tile(UA, G.A, G.ka, G.a_klin, k0, G.K, G.a_kvec, st);
+            issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + 2 * TILE_BYTES);
+        };
+        // prologue: LOOKAHEAD k-blocks in flight (one commit group per k-block, empty groups keep the count uniform)
+        for (uint32_t kb = 0; kb < (uint32_t)LOOKAHEAD; kb++) {
+            if (kb < nkb) issue(kb);
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
+        for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+            // k-block kb has landed (this thread's part): low-part pass, hand the stage to the MMA
+            asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
+            const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES;
+            split_tile(UA, st, st + TILE_BYTES);
+            split_tile(UB, st + 2 * TILE_BYTES, st + 3 * TILE_BYTES);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");              // generic-proxy writes -> visible to the MMA
+            mbar_arrive(smem_u32(&S.full[kb % STAGES]));
+            // then refill the stage the MMA finished longest ago; its copies have two MMA times to land
+            const uint32_t nxt = kb + LOOKAHEAD;
+            if (nxt < nkb) {
+                const uint32_t use = nxt / STAGES;                       // stage (nxt % STAGES) was last read by k-block nxt - STAGES
+                if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[nxt % STAGES]), (use - 1) & 1u, abort_flag);
+                if (ok) issue(nxt);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         // ================= epilogue =================
         if (ok) ok = mbar_wait(smem_u32(&S.accum), 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);                                 // tcgen05.ld needs the whole warp

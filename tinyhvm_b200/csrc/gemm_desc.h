@@ -29,6 +29,7 @@ struct GemmDesc {
     const int32_t *ka, *kb;            // per-k element offsets (device tables, K rounded up to 32 entries)
     uint32_t a_kfast, a_kvec;          // A tile: threads run along k (else along m); 16-byte loads along k legal
     uint32_t b_kfast, b_kvec;
+    long long a_klin, b_klin;          // non-zero: the operand's k offset is k * klin (one reduced dim, no table lookup)
     uint32_t c_nvec;                   // C: n is contiguous and 16-byte aligned per row
     uint32_t kb_chunk;                 // k-blocks (of 32) per split; gridDim.z splits share one output tile
     float *partial;                    // split-K: dense [split][M][N] partial sums (library scratch), else null
