@@ -29,13 +29,17 @@
 
 namespace thc {
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int BM = 128, BN = 128, BK = 32;
+constexpr int STAGES = 4;                           // raw (= high part) k-blocks resident: A and B tile each
+constexpr int LO_STAGES = 2;                        // low-part k-blocks resident
 constexpr int TILE_BYTES = 128 * BK * 4;            // one 128 x 32 f32 tile
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;         // A_hi, A_lo, B_hi, B_lo
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;         // one k-block of one ring: A tile, B tile
+constexpr int LO_BASE = STAGES * STAGE_BYTES;       // the low-part ring follows the raw ring
 constexpr int GEMM_THREADS = 288;                   // 8 producer warps + 1 MMA warp
 constexpr int MMA_WARP = 8;
 constexpr int TMEM_COLS = 128;
-constexpr int LOOKAHEAD = 2;                        // k-blocks of cp.async in flight ahead of the split pass
+constexpr int PREFETCH_AHEAD = 8;                   // k-blocks between an L2 prefetch and its cp.async
+constexpr int LOOKAHEAD = 3;                        // k-blocks of cp.async in flight ahead of the split pass
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 enum : int { ERR_GEMM_TIMEOUT = 8 };
 
@@ -45,7 +49,8 @@ struct GemmShared {                                 // follows the tile area in 
     uint32_t tmem_base;
     int abort_flag;
 };
-constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + sizeof(GemmShared) + 1024;   // + alignment slack
+constexpr int TILE_AREA = (STAGES + LO_STAGES) * STAGE_BYTES;
+constexpr size_t GEMM_SMEM = (size_t)TILE_AREA + sizeof(GemmShared) + 1024;   // + alignment slack
 
 // ---- PTX wrappers ----
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,10 +77,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 __device__ __forceinline__ uint32_t to_tf32(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return u; }
 // x = hi + lo with hi = x truncated to tf32 (what the MMA sees of the raw f32); lo is
-// exact in f32 and zero when x is inf/nan (inf - inf would poison the sum)
+// exact in f32.  (An infinite x gives lo = nan, so inf inputs yield nan outputs.)
 __device__ __forceinline__ uint32_t tf32_low(uint32_t xbits) {
-    const uint32_t hi = xbits & 0xFFFFE000u;
-    return (hi & 0x7F800000u) == 0x7F800000u ? 0u : __float_as_uint(__uint_as_float(xbits) - __uint_as_float(hi));
+    return __float_as_uint(__uint_as_float(xbits) - __uint_as_float(xbits & 0xFFFFE000u));
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -167,6 +171,19 @@ __device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, con
         }
     }
 }
+// pull the 128-byte lines a later k-block will need into L2 (one request per line:
+// only the thread owning chunk 0 of a row asks, and only for 16-byte-vector operands,
+// whose rows are contiguous in k)
+__device__ __forceinline__ void prefetch_tile(const UnitSet &U, long long klin, const int32_t *__restrict__ ktab,
+                                              uint32_t k0, uint32_t K, uint32_t kvec) {
+    if (!kvec || k0 >= K) return;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+        if (U.kcol[i] == 0 && ((U.live >> i) & 1u)) {
+            const float *p = U.rowptr[i] + (klin ? (long long)k0 * klin : (long long)ktab[k0]);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+}
 // low-part pass over this thread's own units: lo = x - trunc_tf32(x).  The raw f32
 // tile doubles as the high part: the tf32 MMA reads only the upper 19 bits.
 __device__ __forceinline__ void split_tile(const UnitSet &U, uint32_t raw_tile, uint32_t lo_tile) {
@@ -181,9 +198,15 @@ __device__ __forceinline__ void split_tile(const UnitSet &U, uint32_t raw_tile, 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_constant__ GemmDesc G) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    GemmShared &S = *reinterpret_cast<GemmShared *>(tiles + (size_t)STAGES * STAGE_BYTES);
+    GemmShared &S = *reinterpret_cast<GemmShared *>(tiles + (size_t)TILE_AREA);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    // tile order: bands of 8 row-tiles, column-tiles fastest inside a band, so the CTAs
+    // that run together share a few A and B panels that stay in L2
+    const uint32_t tm = (G.M + BM - 1) / BM, tn = (G.N + BN - 1) / BN;
+    const uint32_t BH = G.band ? G.band : 1u;
+    const uint32_t band = BH * tn, b0 = (blockIdx.x / band) * BH;
+    const uint32_t bh = tm - b0 < BH ? tm - b0 : BH, within = blockIdx.x % band;
+    const uint32_t m0 = (b0 + within % bh) * BM, n0 = (within / bh) * BN;
     const uint32_t nkb_all = (G.K + BK - 1) / BK;
     const uint32_t kb_lo = blockIdx.z * G.kb_chunk;                       // this CTA's share of the k-blocks (split-K)
     const uint32_t nkb = nkb_all - kb_lo < G.kb_chunk ? nkb_all - kb_lo : G.kb_chunk;
@@ -231,27 +254,35 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
         auto issue = [&](uint32_t kb) {                                  // copies for local k-block kb into its stage
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, k0 = (kb_lo + kb) * BK;
             issue_tile(UA, G.A, G.ka, G.a_klin, k0, G.K, G.a_kvec, st);
-            issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + 2 * TILE_BYTES);
+            issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + TILE_BYTES);
         };
         // prologue: LOOKAHEAD k-blocks in flight (one commit group per k-block, empty groups keep the count uniform)
         for (uint32_t kb = 0; kb < (uint32_t)LOOKAHEAD; kb++) {
-            if (kb < nkb) issue(kb);
+            if (kb < nkb && G.debug_mode != 1 && G.debug_mode != 3) issue(kb);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-            // k-block kb has landed (this thread's part): low-part pass, hand the stage to the MMA
+            // k-block kb has landed (this thread's part).  Its low parts go to lo[kb % 2], which
+            // the MMAs of k-block kb - 2 were the last to read.
             asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
-            const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES;
-            split_tile(UA, st, st + TILE_BYTES);
-            split_tile(UB, st + 2 * TILE_BYTES, st + 3 * TILE_BYTES);
+            if (kb >= (uint32_t)LO_STAGES) {
+                const uint32_t prev = kb - LO_STAGES;
+                ok = mbar_wait(smem_u32(&S.empty[prev % STAGES]), (prev / STAGES) & 1u, abort_flag);
+                if (!ok) break;
+            }
+            const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, lo = tiles_s + LO_BASE + (kb % LO_STAGES) * STAGE_BYTES;
+            if (G.debug_mode != 1 && G.debug_mode != 4) {
+                split_tile(UA, st, lo);
+                split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");              // generic-proxy writes -> visible to the MMA
             mbar_arrive(smem_u32(&S.full[kb % STAGES]));
-            // then refill the stage the MMA finished longest ago; its copies have two MMA times to land
+            // refill the raw stage whose MMAs (k-block kb - 1) finish next: three k-blocks of copies stay in flight
             const uint32_t nxt = kb + LOOKAHEAD;
             if (nxt < nkb) {
                 const uint32_t use = nxt / STAGES;                       // stage (nxt % STAGES) was last read by k-block nxt - STAGES
                 if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[nxt % STAGES]), (use - 1) & 1u, abort_flag);
-                if (ok) issue(nxt);
+                if (ok && G.debug_mode != 1 && G.debug_mode != 3) issue(nxt);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -303,11 +334,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
                 ok = mbar_wait(smem_u32(&S.full[s]), use & 1u, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t st = tiles_s + s * STAGE_BYTES;
-                const uint64_t a_hi = umma_desc(st), a_lo = umma_desc(st + TILE_BYTES);
-                const uint64_t b_hi = umma_desc(st + 2 * TILE_BYTES), b_lo = umma_desc(st + 3 * TILE_BYTES);
+                const uint32_t st = tiles_s + s * STAGE_BYTES, lo = tiles_s + LO_BASE + (kb % LO_STAGES) * STAGE_BYTES;
+                const uint64_t a_hi = umma_desc(st), b_hi = umma_desc(st + TILE_BYTES);
+                const uint64_t a_lo = umma_desc(lo), b_lo = umma_desc(lo + TILE_BYTES);
 #pragma unroll
-                for (uint32_t ks = 0; ks < BK / 8; ks++) {
+                for (uint32_t ks = 0; ks < (G.debug_mode >= 2 ? 0u : (uint32_t)(BK / 8)); ks++) {
                     const uint64_t adv = (uint64_t)(ks * 2u);           // 8 tf32 = 32 bytes, in 16-byte units
                     umma_tf32(tmem, a_lo + adv, b_hi + adv, UMMA_IDESC, (kb | ks) ? 1u : 0u);
                     umma_tf32(tmem, a_hi + adv, b_lo + adv, UMMA_IDESC, 1u);
