@@ -221,6 +221,28 @@ uint64_t thvm_cuda_signature(const thc_fused_op_t *ops, uint32_t n_ops,
                              const thc_tracker_t *const *leaf_sts, uint32_t n_leaves,
                              const thc_shape_t *full_shape, const thc_reduce_spec_t *reduce);
 
+/* ---- allocation-free variant (no counterpart in the reference) ----
+ * out[c] = sum over b and i of x[b][c][i] for a contiguous f32 tensor x[B][C][HW]
+ * (the batch-norm channel statistic), computed by the same split reduce kernels
+ * as thvm_cuda_dispatch_kernel_rs but without touching any allocator: the
+ * partial sums go to a 256 KiB array that is part of the library image, so the
+ * call is usable where allocating is forbidden — inside a host that owns all
+ * device memory through its own arena, while a step is being recorded for
+ * replay, or in a loop that must not stall on an allocator.  `x` and `out` are
+ * device pointers owned by the caller, `stream` a cudaStream_t (NULL = default
+ * stream).  The library need not be initialised.
+ *   - C may not exceed 65536 (the number of partial sums the array holds);
+ *     larger shapes are rejected with return code 1 and a message in
+ *     thvm_cuda_last_error(); 2 = CUDA error, 3 = bad argument, 0 = launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before recording a stream.
+ *   - All calls on a device share the array and it keeps the previous call's
+ *     contents; every slot is rewritten before it is read, so no clearing is
+ *     needed, but two calls whose kernels overlap on the GPU (different
+ *     streams) race on it — serialise them. */
+int      thvm_cuda_channel_sums_noalloc(const float *x, float *out, uint32_t B, uint32_t C, uint32_t HW, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -64,6 +64,7 @@ SYMBOLS = {
     "thvm_cuda_launch_count": (_u64, []),
     "thvm_cuda_last_plan": (C.c_char_p, []),
     "thvm_cuda_set_force_generic": (None, [C.c_int]),
+    "thvm_cuda_channel_sums_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _vp]),
     "thvm_cuda_signature": (_u64, [C.POINTER(abi.FusedOp), _u32, C.POINTER(_PV), _vp, _u32,
                                    C.POINTER(abi.Shape), C.POINTER(abi.ReduceSpec)]),
 }

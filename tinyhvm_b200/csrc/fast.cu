@@ -545,3 +545,88 @@ bool launch_fast(Plan *p, const GenArgs &args) {
 }
 
 }  // namespace thc
+
+// ------------------------------------------------------------------ allocation-free entry point
+// Per-channel sum of a contiguous [B, C, HW] f32 tensor (the batch-norm statistic,
+// SUM over axes 0 and 2) for callers that must not allocate device memory while
+// they run: a host that hands every byte of the GPU to its own arena up front, a
+// step that is being recorded and therefore may not call the allocator, a
+// latency-critical loop that cannot afford an allocator round trip.  The split
+// reduce above normally takes its partial sums from pool scratch
+// (cudaMallocAsync); here they live in a fixed array inside the library image,
+// which every GPU that loads the library carries until the process exits.
+namespace thc {
+
+constexpr unsigned NOALLOC_MAX_PARTIALS = 65536;                 // floats: 256 KiB per GPU
+static __device__ __align__(256) float noalloc_partials[NOALLOC_MAX_PARTIALS];
+
+// `noalloc_partials` is only a host-side handle in host code; the device address
+// has to be asked for, once per device, with that device current.
+struct NoAllocDevice { float *scratch; int sm_count; bool ready; };
+static NoAllocDevice noalloc_dev[64];
+
+static int noalloc_setup(int dev) {
+    NoAllocDevice &d = noalloc_dev[dev];
+    if (d.ready) return 0;
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, noalloc_partials);
+    if (e != cudaSuccess || !p) { cudaGetLastError(); set_error("channel_sums_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e)); return 2; }
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || sms <= 0) { cudaGetLastError(); set_error("channel_sums_noalloc: device attribute query: %s", cudaGetErrorString(e)); return 2; }
+    d.scratch = (float *)p; d.sm_count = sms; d.ready = true;
+    return 0;
+}
+
+}  // namespace thc
+
+extern "C" int thvm_cuda_channel_sums_noalloc(const float *x, float *out, uint32_t B, uint32_t C, uint32_t HW, void *stream) {
+    using namespace thc;
+    if (!x || !out || B == 0 || C == 0 || HW == 0) { set_error("channel_sums_noalloc: null pointer or empty shape"); return 3; }
+    if (C > NOALLOC_MAX_PARTIALS) {
+        set_error("channel_sums_noalloc: %u channels exceed the built-in scratch of %u partial sums", C, NOALLOC_MAX_PARTIALS);
+        return 1;
+    }
+    const unsigned long long n_red = (unsigned long long)B * HW, numel = n_red * C;
+    if (n_red > 0xFFFFFFFFull || numel > (1ull << 40)) { set_error("channel_sums_noalloc: %llu elements per channel is out of range", n_red); return 1; }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); set_error("channel_sums_noalloc: no current CUDA device"); return 2; }
+    if (int rc = noalloc_setup(dev)) return rc;
+    const NoAllocDevice &nd = noalloc_dev[dev];
+
+    // [B, C, HW] with dims 0 and 2 reduced; the leaf is laid out exactly like the iteration space
+    FDesc D;
+    memset(&D, 0, sizeof D);
+    D.rank = 3; D.dims[0] = B; D.dims[1] = C; D.dims[2] = HW;
+    D.is_red[0] = 1; D.is_red[2] = 1;
+    D.n_k = 1; D.kd[0] = 1; D.n_r = 2; D.rd[0] = 0; D.rd[1] = 2;
+    D.numel = numel; D.n_out = C; D.n_red = n_red; D.rtype = THC_SUM;
+    D.fstride[2] = 1; D.fstride[1] = HW; D.fstride[0] = (unsigned long long)C * HW;
+    const bool vec = HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    D.vec = vec ? 4u : 1u;
+    D.prog.n_leaves = 1; D.prog.n_ops = 0; D.chain = 6;
+    FLeaf &L = D.leaf[0];
+    L.ptr = x; L.off = 0; L.mode = 1; L.vec = vec ? 1u : 0u;
+    L.stride[0] = (int)((unsigned long long)C * HW > 0x7FFFFFFFull ? 0 : C * HW); L.stride[1] = (int)HW; L.stride[2] = 1;
+    // split every channel across enough CTAs to fill the GPU, within the scratch size
+    const unsigned long long items = n_red / D.vec;
+    unsigned long long split = ((unsigned long long)4 * nd.sm_count + C - 1) / C;
+    if (split > items / 1024) split = items / 1024;
+    if (split > NOALLOC_MAX_PARTIALS / C) split = NOALLOC_MAX_PARTIALS / C;
+    if (split < 1) split = 1;
+    D.split = (unsigned)split;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned long long groups = (unsigned long long)C * D.split;
+    const unsigned cap = (unsigned)nd.sm_count * 8u;
+    const unsigned grid = (unsigned)(groups < cap ? groups : cap);
+    // Every (channel, split) slot of the scratch is written before the second pass
+    // reads it, so nothing has to be cleared between calls.
+    float *dst = D.split > 1 ? nd.scratch : out;
+    if (D.vec == 4) k_red_inner<StaticEval<6>, 256, 4><<<grid, 256, 0, s>>>(D, dst);
+    else            k_red_inner<StaticEval<6>, 256, 1><<<grid, 256, 0, s>>>(D, dst);
+    if (D.split > 1) k_red_final<<<(C + 255) / 256, 256, 0, s>>>(nd.scratch, out, C, D.split, THC_SUM);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("channel_sums_noalloc: launch failed: %s", cudaGetErrorString(e)); return 2; }
+    g.launches += D.split > 1 ? 2 : 1;
+    return 0;
+}

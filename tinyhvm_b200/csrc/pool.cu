@@ -326,7 +326,11 @@ const char *thvm_cuda_last_error(void) {
 void thvm_cuda_clear_error(void) { g.last_error.clear(); }
 void *thvm_cuda_stream(void) { return (void *)g.stream; }
 void thvm_cuda_sync(void) { if (g.ready) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
-void *thvm_cuda_buf_ptr(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS) ? g.bufs[id].ptr : nullptr; }
+void *thvm_cuda_buf_ptr(uint32_t id) {
+    if (!(g.ready && id && id < THC_MAX_BUFS)) return nullptr;
+    g.bufs[id].shadow_valid = false;        // the caller may write through the pointer: the host shadow no longer speaks for it
+    return g.bufs[id].ptr;
+}
 uint64_t thvm_cuda_buf_bytes(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS && g.bufs[id].ptr) ? g.bufs[id].bytes : 0; }
 uint64_t thvm_cuda_launch_count(void) { return g.launches; }
 const char *thvm_cuda_last_plan(void) { return g.last_plan; }
