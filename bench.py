@@ -43,6 +43,8 @@ ROWS, COLS = 8192, 8192
 FWD_BYTES = 3 * ROWS * COLS * 4 + ROWS * 4
 BWD_BYTES = 4 * ROWS * COLS * 4
 METRIC, UNIT = "fused_kernel_hbm_gbs", "GB/s"
+# measured DRAM traffic per row of the workload (ncu, 2048-row capture): bytes read + written
+NCU_DRAM_BYTES_PER_ROW = {"chain_bwd": (201.375232e6 + 45.099776e6) / 2048, "chain_fwd": (207.519488e6 + 13.173248e6) / 2048}
 WORKLOAD = "cfg2 fused chain f32: y=sum_last(relu(a*b+c)) + VJP wrt a, a,b,c [8192,8192]"
 
 
@@ -62,6 +64,59 @@ def make_inputs(rows: int, cols: int, rank: int):
     from tinyhvm_b200 import synth
     seed = synth.SEED_BASE + 2 + 1000 * rank
     return [synth.normal(seed, t, rows * cols) for t in range(3)]
+
+
+# ------------------------------------------------------------------ config 3: the three GEMMs
+def gemm_dispatches(n: int, A, B, dC):
+    """C = A@B, dA = dC@B^T, dB = A^T@dC as the [M,K,N] MUL + SUM{1} dispatches the
+    reference's scheduler emits (a transposed operand = swapped strides)."""
+    from tinyhvm_b200 import abi
+    from tinyhvm_b200.abi import MUL, SUM, Dispatch, Leaf
+
+    def sv(strides):
+        v = abi.View()
+        v.shape = abi.make_shape([n, n, n])
+        for i, st in enumerate(strides):
+            v.strides[i] = st
+        return abi._finish(v)
+
+    return {
+        "C=A@B": Dispatch([Leaf(A, sv([n, 1, 0])), Leaf(B, sv([0, n, 1]))], [(MUL, 0, 1)], [n, n, n], [1], SUM),
+        "dA=dC@B^T": Dispatch([Leaf(dC, sv([n, 1, 0])), Leaf(B, sv([0, 1, n]))], [(MUL, 0, 1)], [n, n, n], [1], SUM),
+        "dB=A^T@dC": Dispatch([Leaf(A, sv([1, n, 0])), Leaf(dC, sv([0, n, 1]))], [(MUL, 0, 1)], [n, n, n], [1], SUM),
+    }
+
+
+def gemm_section(be, stream, n: int, iters: int = 10):
+    """Time the three config-3 GEMMs (inputs resident); returns per-GEMM ms and TFLOP/s
+    of algorithmic f32 flops (2 n^3), plus the error of a row block against float64."""
+    import torch
+    from tinyhvm_b200 import synth
+    seed = synth.SEED_BASE + 3
+    A, B, dC = (synth.normal(seed, t, n * n) / np.float32(np.sqrt(n)) for t in range(3))
+    ds = gemm_dispatches(n, A, B, dC)
+    ids = {k: be.upload(v) for k, v in (("A", A), ("B", B), ("dC", dC))}
+    out = be.alloc(n * n * 4)
+    leaf_ids = {"C=A@B": [ids["A"], ids["B"]], "dA=dC@B^T": [ids["dC"], ids["B"]], "dB=A^T@dC": [ids["A"], ids["dC"]]}
+    res = {}
+    for name, d in ds.items():
+        for _ in range(3):
+            be.dispatch_ids(out, leaf_ids[name], d)
+        be.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            be.dispatch_ids(out, leaf_ids[name], d)
+        e1.record(stream)
+        be.sync(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res[name] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9, "plan": be.last_plan()}
+    # accuracy of the last one (dB = A^T @ dC) on its first 32 rows, against float64
+    got = be.read(out, np.float32, n * n).reshape(n, n)[:32]
+    ref = A.reshape(n, n)[:, :32].astype(np.float64).T @ dC.reshape(n, n).astype(np.float64)
+    res["max_err_over_rms"] = float(np.abs(got - ref).max() / np.sqrt((ref ** 2).mean()))
+    be.reset(ids["A"] - 1)
+    return res
 
 
 # ------------------------------------------------------------------ clocks
@@ -154,6 +209,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
+                    help="chain = the headline config; gemm = only the three config-3 GEMMs (profiling captures)")
+    ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -176,6 +234,14 @@ def main():
     be = tinyhvm_b200.CudaBackend()
     lib = be.lib
     stream = torch.cuda.ExternalStream(lib.thvm_cuda_stream(), device=torch.device("cuda", local))
+    if args.workload == "gemm":
+        r = gemm_section(be, stream, args.gemm_size, iters=max(args.steps, 1))
+        if rank == 0:
+            print(json.dumps({"metric": "gemm_3xtf32_tflops", "unit": "TFLOP/s", "n_gpus": world, "dtype": "f32 (3xTF32 on tcgen05)",
+                              "config": {"workload": f"cfg3 GEMMs, n={args.gemm_size}"}, "gemms": r,
+                              "value": min(v["tflops"] for k, v in r.items() if isinstance(v, dict))}))
+        be.shutdown()
+        return
     rows = args.rows
     scale = rows / ROWS
     fwd_bytes, bwd_bytes = 3 * rows * COLS * 4 + rows * 4, 4 * rows * COLS * 4
@@ -283,8 +349,12 @@ def main():
 
         def roof(t):
             ach = t[2] / (t[3] * 1e-3) / 1e9
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+            # profiles/chain_kernels_cfg2.md (taken at 2048 rows; traffic is proportional to rows, scaled here)
+            traffic = NCU_DRAM_BYTES_PER_ROW.get(t[0])
             return {"kernel": f"{t[0]} ({t[1]})", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                    "frac": ach / peak, "traffic": None, "ms_per_launch": t[3], "algorithmic_bytes": t[2], "peak_source": peak_src}
+                    "frac": ach / peak, "traffic": traffic * rows if traffic else None, "ms_per_launch": t[3],
+                    "algorithmic_bytes": t[2], "peak_source": peak_src}
 
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -298,6 +368,8 @@ def main():
             "roofline": roof(dom), "roofline_other": roof(oth),
             "checks": {"y_rows0_3_vs_f64": bool(ok_y), "g_rows0_3_bit_exact": bool(ok_g), "backend_error": err},
         }
+        if world == 1 and rows == ROWS:
+            line["extras"] = {"cfg3_gemm_4096": gemm_section(be, stream, 4096)}
         if not args.no_cpu_baseline and world == 1:
             sample_rows = 512
             sec, kind = cpu_run(sample_rows, [x[: sample_rows * COLS] for x in arrays], repeat=2)
