@@ -221,6 +221,20 @@ uint64_t thvm_cuda_signature(const thc_fused_op_t *ops, uint32_t n_ops,
                              const thc_tracker_t *const *leaf_sts, uint32_t n_leaves,
                              const thc_shape_t *full_shape, const thc_reduce_spec_t *reduce);
 
+/* ---- data parallelism (no vtable slot; the reference has no multi-device code, its
+ * nearest relative is one context per thread, src/parallel/reduce.c:36-60) ----
+ * One process per GPU.  Rank 0 makes a 128-byte token and passes it to the other
+ * ranks out of band; every rank calls dp_init after thvm_cuda_init.
+ * dp_allreduce_sum adds, across ranks and in place, the first counts[i] floats of
+ * each listed buffer (NCCL over NVLink, one group per call, ordered on the
+ * backend's stream after the kernels that wrote them).  All return 0 on success. */
+int      thvm_cuda_dp_unique_id(void *out128);
+int      thvm_cuda_dp_init(int rank, int world, const void *id128);
+int      thvm_cuda_dp_world(void);
+int      thvm_cuda_dp_rank(void);
+int      thvm_cuda_dp_allreduce_sum(const uint32_t *buf_ids, const uint64_t *counts, uint32_t n_bufs);
+void     thvm_cuda_dp_shutdown(void);
+
 /* ---- allocation-free variant (no counterpart in the reference) ----
  * out[c] = sum over b and i of x[b][c][i] for a contiguous f32 tensor x[B][C][HW]
  * (the batch-norm channel statistic), computed by the same split reduce kernels

@@ -83,6 +83,32 @@ static void sgd(TinyHVM *ctx, Term w, Term g_view, f32 lr) {
     thvm_eval(ctx, thvm_assign(ctx, w, op2(ctx, UOP_SUB, w, op2(ctx, UOP_MUL, g_view, scalar(ctx, lr)))));
 }
 
+/* ---- data parallelism: the driver runs on one shard of the batch per process; after
+ * the backward pass it hands the gradient buffers to a hook that sums them across
+ * the processes (NCCL inside libthvm_cuda.so for "cuda"; the CPU tests plug in a
+ * gloo exchange), and the update uses lr / world. ---- */
+typedef int (*DrvDpHook)(const u32 *buf_ids, const u64 *counts, u32 n);
+typedef void (*DrvAfterInit)(void);
+static DrvDpHook drv_dp_hook = NULL;
+static DrvAfterInit drv_after_init = NULL;
+static u32 drv_dp_world = 1;
+void drv_set_dp(u32 world, DrvDpHook hook, DrvAfterInit after_init) { drv_dp_world = world ? world : 1; drv_dp_hook = hook; drv_after_init = after_init; }
+/* host access to a buffer of the default backend, for hooks that exchange through the host */
+void drv_buf_read(TinyHVM *ctx, u32 buf_id, void *out, u64 bytes) { ctx_default_backend(ctx)->buf_read(buf_id, out, bytes); }
+void drv_buf_write(TinyHVM *ctx, u32 buf_id, const void *src, u64 bytes) { ctx_default_backend(ctx)->buf_write(buf_id, src, bytes); }
+static TinyHVM *drv_ctx = NULL;
+TinyHVM *drv_current_ctx(void) { return drv_ctx; }
+
+static void dp_sum_grads(TinyHVM *ctx, const Term *grads, u32 n) {
+    if (!drv_dp_hook || drv_dp_world <= 1) return;
+    u32 ids[32]; u64 counts[32];
+    for (u32 i = 0; i < n && i < 32; i++) {
+        TensorMeta *m = &ctx->tensors[(u32)term_val(grads[i])];
+        ids[i] = m->buf_id; counts[i] = m->view.numel;
+    }
+    if (drv_dp_hook(ids, counts, n) != 0) { fprintf(stderr, "drv: gradient all-reduce failed\n"); exit(1); }
+}
+
 static void keepf(TinyHVM *ctx, const char *fmt, u32 step, Term t) { char nm[64]; snprintf(nm, sizeof nm, fmt, step); keep(ctx, nm, t); }
 
 /* ------------------------------------------------------------------ config 4: LeNet-5 */
@@ -92,6 +118,9 @@ static void keepf(TinyHVM *ctx, const char *fmt, u32 step, Term t) { char nm[64]
 int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 keep_grads) {
     cpu_masked_leaf_workaround(dev);
     TinyHVM *ctx = thvm_init(dev);
+    drv_ctx = ctx;
+    if (drv_after_init) drv_after_init();
+    lr = lr / (f32)drv_dp_world;                     /* gradients are summed over the ranks */
     const f32 *p = params;
     Term W1 = thvm_tensor(ctx, p, SHAPE(6, 1, 5, 5)); p += 150;   Term b1 = thvm_tensor(ctx, p, SHAPE(6)); p += 6;
     Term W2 = thvm_tensor(ctx, p, SHAPE(16, 6, 5, 5)); p += 2400; Term b2 = thvm_tensor(ctx, p, SHAPE(16)); p += 16;
@@ -139,6 +168,7 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
         Term du1 = relu_bwd(ctx, as4(ctx, da1, B, 6, 28, 28), u1);
         Term dW1 = conv_wgrad(ctx, xp, du1, B, 1, 6, 28, 28, 5);
         Term db1 = realize(ctx, sum023(ctx, du1));
+        { Term gr[10] = {dW1, db1, dW2, db2, dW3, db3, dW4, db4, dW5, db5}; dp_sum_grads(ctx, gr, 10); }
         keepf(ctx, "loss%u", s, loss);
         if (s == 0 && keep_grads) {
             keep(ctx, "logits", logits);
@@ -158,6 +188,7 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
     drv_secs = now_s() - t0;
     keep(ctx, "W1", W1); keep(ctx, "b1", b1); keep(ctx, "W2", W2); keep(ctx, "b2", b2); keep(ctx, "W3", W3);
     keep(ctx, "b3", b3); keep(ctx, "W4", W4); keep(ctx, "b4", b4); keep(ctx, "W5", W5); keep(ctx, "b5", b5);
+    drv_ctx = NULL;
     thvm_free(ctx);
     return 0;
 }

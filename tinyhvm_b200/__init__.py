@@ -64,6 +64,12 @@ SYMBOLS = {
     "thvm_cuda_launch_count": (_u64, []),
     "thvm_cuda_last_plan": (C.c_char_p, []),
     "thvm_cuda_set_force_generic": (None, [C.c_int]),
+    "thvm_cuda_dp_unique_id": (C.c_int, [_vp]),
+    "thvm_cuda_dp_init": (C.c_int, [C.c_int, C.c_int, _vp]),
+    "thvm_cuda_dp_world": (C.c_int, []),
+    "thvm_cuda_dp_rank": (C.c_int, []),
+    "thvm_cuda_dp_allreduce_sum": (C.c_int, [C.POINTER(_u32), C.POINTER(_u64), _u32]),
+    "thvm_cuda_dp_shutdown": (None, []),
     "thvm_cuda_channel_sums_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _vp]),
     "thvm_cuda_signature": (_u64, [C.POINTER(abi.FusedOp), _u32, C.POINTER(_PV), _vp, _u32,
                                    C.POINTER(abi.Shape), C.POINTER(abi.ReduceSpec)]),

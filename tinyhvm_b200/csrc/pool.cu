@@ -184,9 +184,11 @@ static void release(uint32_t id) {
 }
 
 void plan_cache_clear(void);   // plan.cu
+void thvm_cuda_dp_shutdown(void);   // dp.cu
 
 void thvm_cuda_shutdown(void) {
     if (!g.ready) return;
+    thvm_cuda_dp_shutdown();
     cudaStreamSynchronize(g.stream);
     for (uint32_t i = 1; i < g.count; i++) if (g.bufs[i].ptr) release(i);
     plan_cache_clear();
