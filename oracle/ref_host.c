@@ -26,7 +26,18 @@
 #include "../tinyhvm_b200/backend_cuda/_.c"
 #include <time.h>
 
-TinyHVM *thvm_init(const char *device) { return thvm_init_device(thvm_init_base, device); }
+#include "ref_trace.c"
+
+TinyHVM *thvm_init(const char *device) {
+    TinyHVM *ctx = thvm_init_device(thvm_init_base, device);
+    if (device && strncmp(device, "record", 6) == 0) {            /* "record" or "record-dry" */
+        tr_dry = strcmp(device, "record-dry") == 0;
+        ctx->backends[THVM_DEV_CUDA] = &rec_backend;
+        ctx->n_backends = THVM_DEV_CUDA + 1;
+        ctx->default_device = THVM_DEV_CUDA;
+    }
+    return ctx;
+}
 
 /* ------------------------------------------------------------------ results */
 #define DRV_MAX 512
@@ -115,6 +126,7 @@ static Term ce_backward(TinyHVM *ctx, Term logits, const u8 *labels, u32 B, u32 
     Term s = realize(ctx, thvm_sum_axes(ctx, e, (u32[]){1}, 1));                             /* [B,1] */
     f32 *oh = calloc((size_t)B * C, 4);
     for (u32 i = 0; i < B; i++) oh[i * C + labels[i]] = 1.0f;
+    rec_note("onehot", 0);
     Term onehot = thvm_tensor(ctx, oh, SHAPE(B, C));
     free(oh);
     Term p = op2(ctx, UOP_DIV, e, thvm_expand(ctx, s, SHAPE(B, C)));

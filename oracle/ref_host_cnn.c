@@ -44,19 +44,23 @@ static Term conv_wgrad(TinyHVM *ctx, Term xp, Term g4, u32 B, u32 Ci, u32 Co, u3
 }
 
 /* gradient w.r.t. the (padded) conv input: full correlation of the K-1 padded
- * upstream gradient with the spatially flipped, channel-transposed weight.  The
- * flip is not expressible as a view (the lowerer rejects negative strides,
- * src/lower/_.c:452-455), so the weight goes through the host, identically for
- * every backend.  Raw result, logical shape [B,Ci,OH+K-1,OW+K-1]. */
+ * upstream gradient with the spatially flipped, channel-transposed weight.  A flip is
+ * not expressible as a view (the lowerer rejects negative strides,
+ * src/lower/_.c:452-455), so it is computed on the device as a contraction with a
+ * constant 0/1 tensor, Wf[c,o,p',q'] = sum_{p,q} W[o,c,p,q] * J[p,q,p',q'] with
+ * J = 1 where p+p' = q+q' = K-1 (exact: one product per output is W*1, the rest W*0),
+ * then permuted and materialised.  Raw result, logical shape [B,Ci,OH+K-1,OW+K-1]. */
 static Term conv_dgrad(TinyHVM *ctx, Term g4, Term W, u32 Ci, u32 Co, u32 K) {
-    f32 *hw = thvm_to_host(ctx, W);
-    f32 *wf = malloc((size_t)Co * Ci * K * K * 4);
-    for (u32 o = 0; o < Co; o++) for (u32 c = 0; c < Ci; c++) for (u32 p = 0; p < K; p++) for (u32 q = 0; q < K; q++)
-        wf[((c * Co + o) * K + (K - 1 - p)) * K + (K - 1 - q)] = hw[((o * Ci + c) * K + p) * K + q];
-    Term tWf = thvm_tensor(ctx, wf, SHAPE(Ci, Co, K, K));
-    free(wf);
+    f32 *J = calloc((size_t)K * K * K * K, 4);
+    for (u32 p = 0; p < K; p++) for (u32 q = 0; q < K; q++) J[((p * K + q) * K + (K - 1 - p)) * K + (K - 1 - q)] = 1.0f;
+    Term tJ = thvm_tensor(ctx, J, SHAPE(1, 1, K, K, K, K));
+    free(J);
+    Term Wr = thvm_expand(ctx, thvm_reshape(ctx, W, SHAPE(Co, Ci, K, K, 1, 1)), SHAPE(Co, Ci, K, K, K, K));
+    Term Jr = thvm_expand(ctx, tJ, SHAPE(Co, Ci, K, K, K, K));
+    Term flipped = realize(ctx, thvm_sum_axes(ctx, op2(ctx, UOP_MUL, Wr, Jr), (u32[]){2, 3}, 2));     /* raw [Co,Ci,1,1,K,K] */
+    Term Wf = realize(ctx, op2(ctx, UOP_ADD, thvm_permute(ctx, as4(ctx, flipped, Co, Ci, K, K), (u32[]){1, 0, 2, 3}, 4), scalar(ctx, 0.f)));
     Term gp = pad_hw(ctx, g4, K - 1);
-    return realize(ctx, thvm_conv2d(ctx, gp, tWf, term_era(), 1, (u32[]){1, 1}, (u32[]){0, 0, 0, 0}));
+    return realize(ctx, thvm_conv2d(ctx, gp, Wf, term_era(), 1, (u32[]){1, 1}, (u32[]){0, 0, 0, 0}));
 }
 
 /* 2x2/2 max-pool forward; raw result [B,C,OH,OW,1,1] */
@@ -80,6 +84,7 @@ static Term relu_bwd(TinyHVM *ctx, Term g, Term u) { return realize(ctx, op2(ctx
 
 /* SGD write-back: w <- w - lr * g  (ASSIGN rule, src/interact/tensor_ops.c:3-160) */
 static void sgd(TinyHVM *ctx, Term w, Term g_view, f32 lr) {
+    rec_note("lr", 0);
     thvm_eval(ctx, thvm_assign(ctx, w, op2(ctx, UOP_SUB, w, op2(ctx, UOP_MUL, g_view, scalar(ctx, lr)))));
 }
 
@@ -100,7 +105,7 @@ static TinyHVM *drv_ctx = NULL;
 TinyHVM *drv_current_ctx(void) { return drv_ctx; }
 
 static void dp_sum_grads(TinyHVM *ctx, const Term *grads, u32 n) {
-    if (!drv_dp_hook || drv_dp_world <= 1) return;
+    if (!drv_dp_hook) return;
     u32 ids[32]; u64 counts[32];
     for (u32 i = 0; i < n && i < 32; i++) {
         TensorMeta *m = &ctx->tensors[(u32)term_val(grads[i])];
@@ -122,14 +127,17 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
     if (drv_after_init) drv_after_init();
     lr = lr / (f32)drv_dp_world;                     /* gradients are summed over the ranks */
     const f32 *p = params;
-    Term W1 = thvm_tensor(ctx, p, SHAPE(6, 1, 5, 5)); p += 150;   Term b1 = thvm_tensor(ctx, p, SHAPE(6)); p += 6;
-    Term W2 = thvm_tensor(ctx, p, SHAPE(16, 6, 5, 5)); p += 2400; Term b2 = thvm_tensor(ctx, p, SHAPE(16)); p += 16;
-    Term W3 = thvm_tensor(ctx, p, SHAPE(400, 120)); p += 48000;   Term b3 = thvm_tensor(ctx, p, SHAPE(120)); p += 120;
-    Term W4 = thvm_tensor(ctx, p, SHAPE(120, 84)); p += 10080;    Term b4 = thvm_tensor(ctx, p, SHAPE(84)); p += 84;
-    Term W5 = thvm_tensor(ctx, p, SHAPE(84, 10)); p += 840;       Term b5 = thvm_tensor(ctx, p, SHAPE(10)); p += 10;
+#define PARAM(name, n, ...) (rec_note(name, 0), p += (n), thvm_tensor(ctx, p - (n), SHAPE(__VA_ARGS__)))
+    Term W1 = PARAM("W1", 150, 6, 1, 5, 5),    b1 = PARAM("b1", 6, 6);
+    Term W2 = PARAM("W2", 2400, 16, 6, 5, 5),  b2 = PARAM("b2", 16, 16);
+    Term W3 = PARAM("W3", 48000, 400, 120),    b3 = PARAM("b3", 120, 120);
+    Term W4 = PARAM("W4", 10080, 120, 84),     b4 = PARAM("b4", 84, 84);
+    Term W5 = PARAM("W5", 840, 84, 10),        b5 = PARAM("b5", 10, 10);
     u32 keep_id = ctx->tensor_count;
     double t0 = now_s();
     for (u32 s = 0; s < steps; s++) {
+        rec_mark("step_begin");
+        rec_note("x", 0);
         Term tx = thvm_tensor(ctx, x + (size_t)s * B * 784, SHAPE(B, 1, 28, 28));
         const u8 *lab = labels + (size_t)s * B;
         /* forward */
@@ -145,6 +153,7 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
         Term u4 = linear_fwd(ctx, a3, W4, b4, B, 84);
         Term a4 = realize(ctx, op1(ctx, UOP_RELU, u4));
         Term logits = linear_fwd(ctx, a4, W5, b5, B, 10);
+        rec_note("onehot", 257);                                             /* the one-hot labels built inside the loss */
         Term loss = realize(ctx, cross_entropy_loss(ctx, logits, (u8 *)lab, B, 10));
         /* backward */
         Term dl = ce_backward(ctx, logits, lab, B, 10);
@@ -169,6 +178,7 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
         Term dW1 = conv_wgrad(ctx, xp, du1, B, 1, 6, 28, 28, 5);
         Term db1 = realize(ctx, sum023(ctx, du1));
         { Term gr[10] = {dW1, db1, dW2, db2, dW3, db3, dW4, db4, dW5, db5}; dp_sum_grads(ctx, gr, 10); }
+        rec_mark("read:loss");
         keepf(ctx, "loss%u", s, loss);
         if (s == 0 && keep_grads) {
             keep(ctx, "logits", logits);
@@ -182,7 +192,9 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
         sgd(ctx, W3, as2(ctx, dW3, 400, 120), lr);     sgd(ctx, b3, as1(ctx, db3, 120), lr);
         sgd(ctx, W4, as2(ctx, dW4, 120, 84), lr);      sgd(ctx, b4, as1(ctx, db4, 84), lr);
         sgd(ctx, W5, as2(ctx, dW5, 84, 10), lr);       sgd(ctx, b5, as1(ctx, db5, 10), lr);
+        rec_mark("read:b5");
         f32 *sync = thvm_to_host(ctx, b5); (void)sync;                       /* drain the device queue before the clock stops */
+        rec_mark("step_end");
         if (s + 1 < steps) { thvm_reset(ctx, keep_id); thvm_sched_reset_runtime(); }
     }
     drv_secs = now_s() - t0;
@@ -191,4 +203,14 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
     drv_ctx = NULL;
     thvm_free(ctx);
     return 0;
+}
+
+/* record `steps` LeNet training steps as a vtable trace (see ref_trace.c); dry = log only */
+int drv_record_lenet(const char *path, u32 dry, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params) {
+    if (rec_open(path)) return 1;
+    drv_set_dp(1, rec_dp_hook, NULL);
+    int rc = drv_lenet(dry ? "record-dry" : "record", B, steps, lr, x, labels, params, 0);
+    drv_set_dp(1, NULL, NULL);
+    rec_close();
+    return rc;
 }

@@ -1,0 +1,127 @@
+"""Trace record / replay.
+
+The reference's host runtime runs the staged LeNet driver on a recording backend
+(oracle/ref_trace.c); the trace is then replayed call by call
+  * through the reference's own CPU backend at the vtable boundary (CPU test):
+    losses and parameters must equal the recorded run bit for bit, which shows the
+    trace and the replayer are faithful;
+  * through libthvm_cuda.so (GPU test): same numbers within the training tolerance.
+Also checked: the steady-state step cycle is identical from step to step (that is
+what makes replaying one recorded cycle for every later step legitimate), and the
+committed full-size trace used by the benchmark parses and has the expected shape.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import hostref
+from test_host_dropin import LENET_NAMES, LENET_SHAPES, lenet_inputs, needs_ref
+from tinyhvm_b200 import replay
+
+_u32, _u64, _vp = C.c_uint32, C.c_uint64, C.c_void_p
+
+
+class RefTarget:
+    """The reference's CPU backend behind its vtable (oracle/_ref/libthvm_cpu_ref.so)."""
+
+    def __init__(self, ref):
+        self.lib = ref.lib
+        self.lib.ref_pool_reset(_u32(0))
+
+    def alloc(self, nbytes): return self.lib.ref_buf_alloc(nbytes)
+    def write(self, i, ptr, nbytes): self.lib.ref_buf_write(i, ptr, nbytes)
+    def read(self, i, ptr, nbytes): self.lib.ref_buf_read(i, ptr, nbytes)
+    def free(self, i): pass
+    def incref(self, i): pass
+    def decref(self, i): pass
+    def set_persistent(self, m): pass
+    def allreduce(self, ids, counts): pass
+    def pool_reset(self, keep): self.lib.ref_pool_reset(_u32(keep))
+
+    def copy(self, d, s, nbytes):
+        tmp = np.empty(nbytes, dtype=np.uint8)
+        self.lib.ref_buf_read(s, tmp.ctypes.data, nbytes)
+        self.lib.ref_buf_write(d, tmp.ctypes.data, nbytes)
+
+    def dispatch(self, a):
+        self.lib.ref_dispatch_kernel_rs(_u32(a.out), a.ids, a.view_ptrs, a.st_ptrs, _u32(a.n), a.ops, _u32(a.n_ops), C.byref(a.full),
+                                        C.byref(a.red) if a.has_red else None, a.dts, _u32(a.out_dt))
+
+
+def onehot(labels, classes=10):
+    o = np.zeros((labels.size, classes), dtype=np.float32)
+    o[np.arange(labels.size), labels] = 1.0
+    return o.ravel()
+
+
+def record(tmp_path, B, steps, dry=0):
+    x, lab, ps = lenet_inputs(B, steps)
+    path = tmp_path / f"lenet_b{B}.thtr"
+    res = hostref.run("drv_record_lenet", str(path), dry, B, steps, 0.01, x, lab, np.concatenate(ps))
+    return path, res, (x, lab, ps)
+
+
+def replay_lenet(target, recs, B, steps, data, lr=0.01):
+    x, lab, ps = data
+    rp = replay.Replayer(target, recs)
+    rp.run_prefix(dict(zip(LENET_NAMES, ps)))
+    losses = []
+    for s in range(steps):
+        ext = {"x": x[s * B * 784:(s + 1) * B * 784], "onehot": onehot(lab[s * B:(s + 1) * B]),
+               "lr": np.array([lr], dtype=np.float32)}
+        cyc = rp.cycles[min(s, 1)]                        # cycle 0 = first step, cycle 1 = every later step
+        out = rp.run(cyc, ext)
+        losses.append(float(out["loss"][0]))
+    params = {}
+    for k, (name, shape) in enumerate(zip(LENET_NAMES, LENET_SHAPES)):
+        buf = np.empty(int(np.prod(shape)), dtype=np.float32)
+        target.read(k + 1, buf.ctypes.data, buf.nbytes)   # parameters are the first ten buffers of the prefix
+        params[name] = buf
+    return losses, params
+
+
+@needs_ref
+def test_replay_through_reference_cpu_backend_is_bit_exact(tmp_path, ref):
+    B, steps = 8, 4
+    path, res, data = record(tmp_path, B, steps)
+    recs = replay.load_trace(path)
+    prefix, cycles = replay.split_steps(recs)
+    assert len(cycles) == steps
+    key = lambda c: [(r.op, r.f, r.blob) for r in c if r.op != replay.MARK]
+    assert key(cycles[1]) == key(cycles[2]), "the steady-state step cycle changes from step to step"
+    losses, params = replay_lenet(RefTarget(ref), recs, B, steps, data)
+    for s in range(steps):
+        assert losses[s] == float(res[f"loss{s}"][0]), s
+    for n in LENET_NAMES:
+        assert np.array_equal(params[n], res[n]), n
+    ref.lib.ref_pool_reset(_u32(0))
+
+
+def test_committed_lenet_trace_parses():
+    path = replay.TRACE_DIR / "lenet_b1024.thtr.gz"
+    recs = replay.load_trace(path)
+    prefix, cycles = replay.split_steps(recs)
+    assert len(cycles) >= 2
+    n_disp = sum(1 for r in cycles[1] if r.op == replay.DISPATCH)
+    assert 50 <= n_disp <= 80
+    ext = {r.f[3] for r in cycles[1] if r.op == replay.WRITE and r.f[1]}
+    assert ext == {"x", "onehot", "lr"}, ext
+    x_bytes = [r.f[2] for r in cycles[1] if r.op == replay.WRITE and r.f[3] == "x"]
+    assert x_bytes == [1024 * 784 * 4]
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_replay_on_gpu_matches_recorded_run(tmp_path, cuda):
+    B, steps = 8, 3
+    path, res, data = record(tmp_path, B, steps)
+    recs = replay.load_trace(path)
+    cuda.reset(0)
+    losses, params = replay_lenet(replay.CudaTarget(cuda), recs, B, steps, data)
+    for s in range(steps):
+        assert abs(losses[s] - float(res[f"loss{s}"][0])) < 2e-5, s
+    for n in LENET_NAMES:
+        assert np.allclose(params[n], res[n], rtol=1e-4, atol=1e-6), n
+    cuda.reset(0)
+    assert cuda.last_error() == ""
