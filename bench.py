@@ -119,6 +119,74 @@ def gemm_section(be, stream, n: int, iters: int = 10):
     return res
 
 
+# ------------------------------------------------------------------ config 4: LeNet-5 training steps (trace replay)
+LENET_SHAPES = [(6, 1, 5, 5), (6,), (16, 6, 5, 5), (16,), (400, 120), (120,), (120, 84), (84,), (84, 10), (10,)]
+LENET_FAN_IN = [25, 25, 150, 150, 400, 400, 120, 120, 84, 84]
+LENET_NAMES = ["W1", "b1", "W2", "b2", "W3", "b3", "W4", "b4", "W5", "b5"]
+
+
+def lenet_section(be, stream, rank: int, world: int, steps: int = 10, global_batch: int = 1024):
+    """LeNet-5 SGD steps at a fixed global batch, batch-sharded over the ranks: every rank replays the
+    recorded step program of its shard size (tinyhvm_b200/traces, the vtable calls the reference's
+    scheduler makes for the staged LeNet step) against the C ABI; gradients are summed with
+    thvm_cuda_dp_allreduce_sum and the update uses lr / world.  Each step uploads its batch and
+    one-hot labels from host memory and reads the loss back, so the rate is end to end."""
+    import torch
+    import torch.distributed as dist
+    from tinyhvm_b200 import replay, synth
+    B = global_batch // world
+    recs = replay.load_trace(replay.TRACE_DIR / f"lenet_b{B}.thtr.gz")
+    lib = be.lib
+    if world > 1:
+        token = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            raw = (C.c_uint8 * 128)()
+            assert lib.thvm_cuda_dp_unique_id(raw) == 0, be.last_error()
+            token = torch.tensor(list(raw), dtype=torch.uint8, device="cuda")
+        dist.broadcast(token, 0)
+        raw = (C.c_uint8 * 128)(*token.cpu().tolist())
+        assert lib.thvm_cuda_dp_init(rank, world, raw) == 0, be.last_error()
+    be.reset(0)
+    seed = synth.SEED_BASE + 4
+    ps = [synth.kaiming_uniform(seed, 10 + i, int(np.prod(sh)), f) for i, (sh, f) in enumerate(zip(LENET_SHAPES, LENET_FAN_IN))]
+    rp = replay.Replayer(replay.CudaTarget(be), recs)
+    rp.run_prefix(dict(zip(LENET_NAMES, ps)))
+    n_data = 4                                             # distinct synthetic batches, cycled
+    xs = [torch.from_numpy(synth.uniform(seed, 100 + 8 * k + rank, B * 784)).pin_memory() for k in range(n_data)]
+    ohs = []
+    for k in range(n_data):
+        lab = synth.labels(seed, 200 + 8 * k + rank, B, 10)
+        o = np.zeros((B, 10), dtype=np.float32); o[np.arange(B), lab] = 1.0
+        ohs.append(torch.from_numpy(o.ravel()).pin_memory())
+    lr = np.array([0.01 / world], dtype=np.float32)
+
+    def one(k, cyc):
+        return rp.run(cyc, {"x": xs[k % n_data].numpy(), "onehot": ohs[k % n_data].numpy(), "lr": lr})
+
+    losses = [float(one(0, rp.cycles[0])["loss"][0])]      # first step: plans are built here
+    for k in range(1, 4):
+        losses.append(float(one(k, rp.cycles[1])["loss"][0]))
+    if world > 1:
+        dist.barrier()
+    be.sync(); torch.cuda.synchronize()
+    launches0 = be.launches()
+    t0 = time.perf_counter()
+    for k in range(steps):
+        losses.append(float(one(4 + k, rp.cycles[1])["loss"][0]))
+    be.sync(); torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    launches = (be.launches() - launches0) // steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    be.reset(0)
+    return {"samples_per_s": global_batch / (ms * 1e-3), "ms_per_step": ms, "global_batch": global_batch, "per_rank_batch": B,
+            "dispatches_per_step": rp.n_dispatches(rp.cycles[1]), "kernel_launches_per_step": int(launches),
+            "h2d_bytes_per_step": int(B * 784 * 4 + 2 * B * 40), "loss_first": losses[0], "loss_last": losses[-1],
+            "error": be.last_error()}
+
+
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
@@ -209,8 +277,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm"],
-                    help="chain = the headline config; gemm = only the three config-3 GEMMs (profiling captures)")
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "lenet"],
+                    help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet = only the config-4 training steps")
     ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -241,6 +309,17 @@ def main():
                               "config": {"workload": f"cfg3 GEMMs, n={args.gemm_size}"}, "gemms": r,
                               "value": min(v["tflops"] for k, v in r.items() if isinstance(v, dict))}))
         be.shutdown()
+        return
+    if args.workload == "lenet":
+        r = lenet_section(be, stream, rank, world, steps=max(args.steps, 1))
+        if rank == 0:
+            print(json.dumps({"metric": "lenet_train_samples_per_s", "unit": "samples/s", "value": r["samples_per_s"], "n_gpus": world,
+                              "scaling": "strong", "dtype": "f32", "data": "synthetic",
+                              "config": {"workload": "cfg4 LeNet-5 SGD step, global batch 1024, trace replay", "parallelism": f"dp{world}"},
+                              "lenet": r}))
+        be.shutdown()
+        if world > 1:
+            dist.destroy_process_group()
         return
     rows = args.rows
     scale = rows / ROWS
@@ -337,6 +416,12 @@ def main():
     ok_y = np.allclose(y[:4], y_ref, rtol=1e-5)
     err = be.last_error()
 
+    lenet = None
+    if rows == ROWS:                                       # every rank takes part (gradient all-reduce at N > 1)
+        try:
+            lenet = lenet_section(be, stream, rank, world)
+        except Exception as ex:                            # an extra: never lose the headline line over it
+            lenet = {"error": repr(ex)}
     if rank == 0:
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
@@ -368,8 +453,9 @@ def main():
             "roofline": roof(dom), "roofline_other": roof(oth),
             "checks": {"y_rows0_3_vs_f64": bool(ok_y), "g_rows0_3_bit_exact": bool(ok_g), "backend_error": err},
         }
+        line["extras"] = {"cfg4_lenet_train": lenet}
         if world == 1 and rows == ROWS:
-            line["extras"] = {"cfg3_gemm_4096": gemm_section(be, stream, 4096)}
+            line["extras"]["cfg3_gemm_4096"] = gemm_section(be, stream, 4096)
         if not args.no_cpu_baseline and world == 1:
             sample_rows = 512
             sec, kind = cpu_run(sample_rows, [x[: sample_rows * COLS] for x in arrays], repeat=2)

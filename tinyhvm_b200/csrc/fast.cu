@@ -524,6 +524,15 @@ bool launch_fast(Plan *p, const GenArgs &args) {
     }
     float *out = (float *)args.out;
     if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return false;
+    if (g.profile_level >= 2) {
+        int w = snprintf(g.last_shape, sizeof g.last_shape, "dims=[");
+        for (unsigned d = 0; d < D.rank; d++) w += snprintf(g.last_shape + w, sizeof g.last_shape - w, "%u%s%s", D.dims[d], D.is_red[d] ? "r" : "", d + 1 < D.rank ? "," : "");
+        w += snprintf(g.last_shape + w, sizeof g.last_shape - w, "] vec=%u leaves:", D.vec);
+        for (unsigned i = 0; i < D.prog.n_leaves; i++) {
+            w += snprintf(g.last_shape + w, sizeof g.last_shape - w, " m%u(", D.leaf[i].mode);
+            for (unsigned d = 0; d < D.rank; d++) w += snprintf(g.last_shape + w, sizeof g.last_shape - w, "%d%s", D.leaf[i].stride[d], d + 1 < D.rank ? "," : ")");
+        }
+    }
     profile_begin();
     switch (D.chain) {
         case 1: launch_with<StaticEval<1>>(F, D, out); break;

@@ -80,6 +80,7 @@ void after_launch(const char *plan) {
             THC_CUDA_OK(cudaEventSynchronize(prof_ev[1]));
             float ms = 0; THC_CUDA_OK(cudaEventElapsedTime(&ms, prof_ev[0], prof_ev[1]));
             s.ms += ms; prof_open = false;
+            if (g.profile_level >= 2 && ms > 0.1f) fprintf(stderr, "thvm_cuda slow launch: %-22s %8.3f ms  %s\n", plan, ms, g.last_shape);
         }
     }
 }
@@ -172,6 +173,7 @@ int thvm_cuda_init(void) {
     g.scratch = nullptr; g.scratch_bytes = 0;
     g.launches = 0; g.last_plan = ""; g.last_error.clear();
     g.profile = getenv("THVM_PROFILE") != nullptr;
+    g.profile_level = g.profile ? atoi(getenv("THVM_PROFILE")) : 0;
     g.ready = true;
     return 0;
 }
