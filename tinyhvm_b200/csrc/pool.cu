@@ -15,9 +15,11 @@
 //     (Metal pool: src/backend/metal/pool.m:144-152).
 // Memory comes from the device's stream-ordered pool (cudaMallocAsync) with the
 // release threshold lifted, so a training step recycles its buffers without
-// going back to the driver.  Buffers of <= 256 bytes written by the host (the
-// reference turns every shape/axes/scalar constant into such a buffer) keep a
-// host shadow, so reading them back never waits for the GPU.
+// going back to the driver.  Buffers of <= 256 bytes (the reference turns every
+// shape / axes / scalar constant into such a buffer, hundreds per training step)
+// start out as a host shadow only: no allocation, no copy, and reading them back
+// never waits for the GPU.  Device memory is attached, and the shadow uploaded,
+// the first time a kernel or a device copy actually touches the buffer.
 #include <stdarg.h>
 #include <string.h>
 #include <map>
@@ -44,11 +46,31 @@ void fatal(const char *fmt, ...) {
     exit(1);   // the reference's backends exit on unrecoverable errors too (src/backend/metal/pool.m:49-53)
 }
 
-Buf &buf_checked(uint32_t id, const char *who) {
+Buf &buf_live(uint32_t id, const char *who) {
     if (!g.ready) fatal("%s: backend not initialised (no CUDA device?)", who);
-    if (id == 0 || id >= THC_MAX_BUFS || g.bufs[id].ptr == nullptr)
+    if (id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].live)
         fatal("%s: buffer id %u is not live", who, id);
     return g.bufs[id];
+}
+
+static uint8_t *ring_take(uint64_t bytes);
+
+Buf &buf_checked(uint32_t id, const char *who) {
+    Buf &b = buf_live(id, who);
+    if (!b.ptr) {                                   // host-only so far: attach device memory now
+        uint64_t sz = (b.bytes + 15) & ~15ull;
+        if (sz == 0) sz = 16;
+        THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
+        if (b.shadow && b.shadow_valid && b.bytes) {
+            uint8_t *stage = ring_take(sz);
+            memset(stage, 0, sz);
+            memcpy(stage, b.shadow, b.bytes);
+            THC_CUDA_OK(cudaMemcpyAsync(b.ptr, stage, sz, cudaMemcpyHostToDevice, g.stream));
+        } else {
+            THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.stream));
+        }
+    }
+    return b;
 }
 
 void *scratch_reserve(uint64_t bytes) {
@@ -192,7 +214,7 @@ void thvm_cuda_shutdown(void) {
     if (!g.ready) return;
     thvm_cuda_dp_shutdown();
     cudaStreamSynchronize(g.stream);
-    for (uint32_t i = 1; i < g.count; i++) if (g.bufs[i].ptr) release(i);
+    for (uint32_t i = 1; i < g.count; i++) if (g.bufs[i].live) release(i);
     plan_cache_clear();
     if (g.scratch) cudaFreeAsync(g.scratch, g.stream);
     g.scratch = nullptr; g.scratch_bytes = 0;
@@ -208,38 +230,39 @@ void thvm_cuda_shutdown(void) {
 uint32_t thvm_cuda_buf_alloc(uint64_t bytes) {
     if (!g.ready) fatal("buf_alloc: backend not initialised (no CUDA device?)");
     if (g.count >= THC_MAX_BUFS) { set_error("buf_alloc: id space exhausted (%u)", THC_MAX_BUFS); return 0; }
-    uint64_t sz = (bytes + 15) & ~15ull;
-    if (sz == 0) sz = 16;
     void *p = nullptr;
-    cudaError_t e = cudaMallocAsync(&p, sz, g.stream);
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
-        return 0;
+    if (bytes > SHADOW_MAX) {
+        uint64_t sz = (bytes + 15) & ~15ull;
+        cudaError_t e = cudaMallocAsync(&p, sz, g.stream);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+            return 0;
+        }
+        THC_CUDA_OK(cudaMemsetAsync(p, 0, sz, g.stream));
     }
-    THC_CUDA_OK(cudaMemsetAsync(p, 0, sz, g.stream));
     uint32_t id = g.count++;
     Buf &b = g.bufs[id];
-    b.ptr = p; b.bytes = bytes; b.refcount = 1;
+    b.live = true; b.ptr = p; b.bytes = bytes; b.refcount = 1;
     if (bytes <= SHADOW_MAX) {
         b.shadow = (uint8_t *)calloc(1, SHADOW_MAX);
-        b.shadow_valid = true;                     // zeros, like the device copy
+        b.shadow_valid = true;                     // zeros, like a fresh device buffer
     }
     return id;
 }
 
 void thvm_cuda_buf_free(uint32_t id) {
-    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].live) return;
     release(id);
 }
 
 void thvm_cuda_buf_incref(uint32_t id) {
-    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].live) return;
     g.bufs[id].refcount++;
 }
 
 void thvm_cuda_buf_decref(uint32_t id) {
-    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].ptr) return;
+    if (!g.ready || id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].live) return;
     if (id <= g.persistent) return;
     Buf &b = g.bufs[id];
     if (b.refcount > 0) b.refcount--;
@@ -252,13 +275,14 @@ void thvm_cuda_mem_checkpoint(uint32_t *leaf_buf_ids, uint32_t n_leaves) {
 void thvm_cuda_buf_mark_use(uint32_t id) { (void)id; }
 
 void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
-    Buf &b = buf_checked(id, "buf_write");
+    Buf &b = buf_live(id, "buf_write");
     if (bytes > b.bytes) {
         set_error("buf_write: %llu bytes into buffer %u of %llu", (unsigned long long)bytes, id, (unsigned long long)b.bytes);
         bytes = b.bytes;
     }
     if (bytes == 0) return;
     if (b.shadow) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
+    if (!b.ptr) return;                            // host-only buffer: uploaded if and when the device needs it
     if (bytes <= RING_MAX_MSG) {
         uint8_t *stage = ring_take(bytes);
         memcpy(stage, data, bytes);
@@ -273,11 +297,12 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
 }
 
 static void read_impl(uint32_t id, void *out, uint64_t bytes, bool sync) {
-    Buf &b = buf_checked(id, "buf_read");
+    Buf &b = buf_live(id, "buf_read");
     uint64_t n = bytes < b.bytes ? bytes : b.bytes;
     if (bytes > n) memset((uint8_t *)out + n, 0, bytes - n);   // past the end reads as zero (src/backend/metal/pool.m:214-218)
     if (n == 0) return;
     if (b.shadow && b.shadow_valid) { memcpy(out, b.shadow, n); return; }
+    if (!b.ptr) { memset(out, 0, n); return; }
     THC_CUDA_OK(cudaMemcpyAsync(out, b.ptr, n, cudaMemcpyDeviceToHost, g.stream));
     if (sync) check_device_status("buf_read");                // drains the stream
 }
@@ -287,6 +312,12 @@ void thvm_cuda_buf_read(uint32_t id, void *out, uint64_t bytes) { read_impl(id, 
 void thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, false); }
 
 void thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes) {
+    Buf &dl = buf_live(dst_buf, "buf_copy(dst)");
+    Buf &sl = buf_live(src_buf, "buf_copy(src)");
+    if (!dl.ptr && !sl.ptr && dl.shadow && sl.shadow && sl.shadow_valid && nbytes <= dl.bytes && nbytes <= sl.bytes) {
+        memcpy(dl.shadow, sl.shadow, nbytes); dl.shadow_valid = true;      // both still host-only
+        return;
+    }
     Buf &d = buf_checked(dst_buf, "buf_copy(dst)");
     Buf &s = buf_checked(src_buf, "buf_copy(src)");
     uint64_t n = nbytes;
@@ -305,7 +336,7 @@ void thvm_cuda_pool_reset(uint32_t keep) {
     if (!g.ready) return;
     uint32_t first = keep + 1;
     if (first < 1) first = 1;
-    for (uint32_t i = first; i < g.count; i++) if (g.bufs[i].ptr) release(i);
+    for (uint32_t i = first; i < g.count; i++) if (g.bufs[i].live) release(i);
     if (first < g.count) g.count = first;
 }
 
@@ -331,11 +362,12 @@ void thvm_cuda_clear_error(void) { g.last_error.clear(); }
 void *thvm_cuda_stream(void) { return (void *)g.stream; }
 void thvm_cuda_sync(void) { if (g.ready) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
 void *thvm_cuda_buf_ptr(uint32_t id) {
-    if (!(g.ready && id && id < THC_MAX_BUFS)) return nullptr;
-    g.bufs[id].shadow_valid = false;        // the caller may write through the pointer: the host shadow no longer speaks for it
-    return g.bufs[id].ptr;
+    if (!(g.ready && id && id < THC_MAX_BUFS && g.bufs[id].live)) return nullptr;
+    Buf &b = buf_checked(id, "buf_ptr");    // attaches device memory if the buffer was host-only
+    b.shadow_valid = false;                 // the caller may write through the pointer: the host shadow no longer speaks for it
+    return b.ptr;
 }
-uint64_t thvm_cuda_buf_bytes(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS && g.bufs[id].ptr) ? g.bufs[id].bytes : 0; }
+uint64_t thvm_cuda_buf_bytes(uint32_t id) { return (g.ready && id && id < THC_MAX_BUFS && g.bufs[id].live) ? g.bufs[id].bytes : 0; }
 uint64_t thvm_cuda_launch_count(void) { return g.launches; }
 const char *thvm_cuda_last_plan(void) { return g.last_plan; }
 void thvm_cuda_set_force_generic(int on) { g.force_generic = on; }

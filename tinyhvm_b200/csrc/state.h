@@ -14,7 +14,8 @@
 namespace thc {
 
 struct Buf {
-    void    *ptr      = nullptr;   // device memory
+    bool     live     = false;     // id handed out and not yet freed
+    void    *ptr      = nullptr;   // device memory; null while a small host-written buffer lives only in its shadow
     uint64_t bytes    = 0;         // size asked for by the caller
     uint32_t refcount = 0;
     uint8_t *shadow   = nullptr;   // host copy of a small host-written buffer
@@ -66,8 +67,10 @@ void set_error(const char *fmt, ...);
                          __FILE__, __LINE__);                                     \
     } while (0)
 
-// a live buffer or a fatal error
+// a live buffer with device memory behind it (materialised on demand), or a fatal error
 Buf &buf_checked(uint32_t id, const char *who);
+// a live buffer that may still be host-only
+Buf &buf_live(uint32_t id, const char *who);
 // scratch of at least `bytes` (stream-ordered reuse: all users run on g.stream)
 void *scratch_reserve(uint64_t bytes);
 // mark a buffer as written by the device
