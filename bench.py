@@ -44,7 +44,7 @@ FWD_BYTES = 3 * ROWS * COLS * 4 + ROWS * 4
 BWD_BYTES = 4 * ROWS * COLS * 4
 METRIC, UNIT = "fused_kernel_hbm_gbs", "GB/s"
 # measured DRAM traffic per row of the workload (ncu, 2048-row capture): bytes read + written
-NCU_DRAM_BYTES_PER_ROW = {"chain_bwd": (201.375232e6 + 45.099776e6) / 2048, "chain_fwd": (207.519488e6 + 13.173248e6) / 2048}
+NCU_DRAM_BYTES_PER_ROW = {"chain_bwd": (201.335552e6 + 46.762240e6) / 2048, "chain_fwd": (201.336576e6 + 4.856576e6) / 2048}
 WORKLOAD = "cfg2 fused chain f32: y=sum_last(relu(a*b+c)) + VJP wrt a, a,b,c [8192,8192]"
 
 
@@ -119,45 +119,57 @@ def gemm_section(be, stream, n: int, iters: int = 10):
     return res
 
 
-# ------------------------------------------------------------------ config 4: LeNet-5 training steps (trace replay)
-LENET_SHAPES = [(6, 1, 5, 5), (6,), (16, 6, 5, 5), (16,), (400, 120), (120,), (120, 84), (84,), (84, 10), (10,)]
-LENET_FAN_IN = [25, 25, 150, 150, 400, 400, 120, 120, 84, 84]
-LENET_NAMES = ["W1", "b1", "W2", "b2", "W3", "b3", "W4", "b4", "W5", "b5"]
+# ------------------------------------------------------------------ configs 4 and 5: CNN training steps (trace replay)
+CNN = {"lenet": {"global_batch": 1024, "in_elems": 784, "classes": 10, "seed_off": 4},
+       "vgg": {"global_batch": 512, "in_elems": 3 * 64 * 64, "classes": 100, "seed_off": 5}}
+_dp_ready = False
 
 
-def lenet_section(be, stream, rank: int, world: int, steps: int = 10, global_batch: int = 1024):
-    """LeNet-5 SGD steps at a fixed global batch, batch-sharded over the ranks: every rank replays the
+def dp_setup(be, rank: int, world: int):
+    """One NCCL communicator per process for the gradient sums; the rendezvous token travels over torch.distributed."""
+    global _dp_ready
+    if world == 1 or _dp_ready:
+        return
+    import torch
+    import torch.distributed as dist
+    lib = be.lib
+    token = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        raw = (C.c_uint8 * 128)()
+        assert lib.thvm_cuda_dp_unique_id(raw) == 0, be.last_error()
+        token = torch.tensor(list(raw), dtype=torch.uint8, device="cuda")
+    dist.broadcast(token, 0)
+    raw = (C.c_uint8 * 128)(*token.cpu().tolist())
+    assert lib.thvm_cuda_dp_init(rank, world, raw) == 0, be.last_error()
+    _dp_ready = True
+
+
+def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: int = 10):
+    """SGD steps of a CNN config at a fixed global batch, batch-sharded over the ranks: every rank replays the
     recorded step program of its shard size (tinyhvm_b200/traces, the vtable calls the reference's
-    scheduler makes for the staged LeNet step) against the C ABI; gradients are summed with
+    scheduler makes for the staged step) against the C ABI; gradients are summed with
     thvm_cuda_dp_allreduce_sum and the update uses lr / world.  Each step uploads its batch and
     one-hot labels from host memory and reads the loss back, so the rate is end to end."""
     import torch
     import torch.distributed as dist
-    from tinyhvm_b200 import replay, synth
+    from tinyhvm_b200 import configs, replay, synth
+    cfg = CNN[model]
+    global_batch, E, classes = cfg["global_batch"], cfg["in_elems"], cfg["classes"]
     B = global_batch // world
-    recs = replay.load_trace(replay.TRACE_DIR / f"lenet_b{B}.thtr.gz")
-    lib = be.lib
-    if world > 1:
-        token = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            raw = (C.c_uint8 * 128)()
-            assert lib.thvm_cuda_dp_unique_id(raw) == 0, be.last_error()
-            token = torch.tensor(list(raw), dtype=torch.uint8, device="cuda")
-        dist.broadcast(token, 0)
-        raw = (C.c_uint8 * 128)(*token.cpu().tolist())
-        assert lib.thvm_cuda_dp_init(rank, world, raw) == 0, be.last_error()
+    recs = replay.load_trace(replay.TRACE_DIR / f"{model}_b{B}.thtr.gz")
+    dp_setup(be, rank, world)
     be.reset(0)
-    seed = synth.SEED_BASE + 4
-    ps = [synth.kaiming_uniform(seed, 10 + i, int(np.prod(sh)), f) for i, (sh, f) in enumerate(zip(LENET_SHAPES, LENET_FAN_IN))]
+    seed = synth.SEED_BASE + cfg["seed_off"]
+    if model == "lenet":
+        names, ps = configs.LENET_NAMES, configs.lenet_params()
+    else:
+        names, ps = configs.vgg_shapes()[1], configs.vgg_params()
     rp = replay.Replayer(replay.CudaTarget(be), recs)
-    rp.run_prefix(dict(zip(LENET_NAMES, ps)))
+    rp.run_prefix(dict(zip(names, ps)))
     n_data = 4                                             # distinct synthetic batches, cycled
-    xs = [torch.from_numpy(synth.uniform(seed, 100 + 8 * k + rank, B * 784)).pin_memory() for k in range(n_data)]
-    ohs = []
-    for k in range(n_data):
-        lab = synth.labels(seed, 200 + 8 * k + rank, B, 10)
-        o = np.zeros((B, 10), dtype=np.float32); o[np.arange(B), lab] = 1.0
-        ohs.append(torch.from_numpy(o.ravel()).pin_memory())
+    gen = synth.uniform if model == "lenet" else synth.normal
+    xs = [torch.from_numpy(gen(seed, 100 + 8 * k + rank, B * E)).pin_memory() for k in range(n_data)]
+    ohs = [torch.from_numpy(configs.onehot(synth.labels(seed, 200 + 8 * k + rank, B, classes), classes)).pin_memory() for k in range(n_data)]
     lr = np.array([0.01 / world], dtype=np.float32)
 
     def one(k, cyc):
@@ -183,7 +195,7 @@ def lenet_section(be, stream, rank: int, world: int, steps: int = 10, global_bat
     be.reset(0)
     return {"samples_per_s": global_batch / (ms * 1e-3), "ms_per_step": ms, "global_batch": global_batch, "per_rank_batch": B,
             "dispatches_per_step": rp.n_dispatches(rp.cycles[1]), "kernel_launches_per_step": int(launches),
-            "h2d_bytes_per_step": int(B * 784 * 4 + 2 * B * 40), "loss_first": losses[0], "loss_last": losses[-1],
+            "h2d_bytes_per_step": int(B * E * 4 + B * classes * 4 + 4), "loss_first": losses[0], "loss_last": losses[-1],
             "error": be.last_error()}
 
 
@@ -277,8 +289,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "lenet"],
-                    help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet = only the config-4 training steps")
+    ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "lenet", "vgg"],
+                    help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet / vgg = only the config-4 / config-5 training steps")
     ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -310,13 +323,14 @@ def main():
                               "value": min(v["tflops"] for k, v in r.items() if isinstance(v, dict))}))
         be.shutdown()
         return
-    if args.workload == "lenet":
-        r = lenet_section(be, stream, rank, world, steps=max(args.steps, 1))
+    if args.workload in CNN:
+        r = cnn_section(be, stream, rank, world, args.workload, steps=max(args.steps, 1))
         if rank == 0:
-            print(json.dumps({"metric": "lenet_train_samples_per_s", "unit": "samples/s", "value": r["samples_per_s"], "n_gpus": world,
+            what = {"lenet": "cfg4 LeNet-5 SGD step, global batch 1024", "vgg": "cfg5 VGG-style CNN SGD step, 64x64 inputs, global batch 512"}
+            print(json.dumps({"metric": f"{args.workload}_train_samples_per_s", "unit": "samples/s", "value": r["samples_per_s"], "n_gpus": world,
                               "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                              "config": {"workload": "cfg4 LeNet-5 SGD step, global batch 1024, trace replay", "parallelism": f"dp{world}"},
-                              "lenet": r}))
+                              "config": {"workload": what[args.workload] + ", trace replay", "parallelism": f"dp{world}"},
+                              "train": r}))
         be.shutdown()
         if world > 1:
             dist.destroy_process_group()
@@ -416,12 +430,14 @@ def main():
     ok_y = np.allclose(y[:4], y_ref, rtol=1e-5)
     err = be.last_error()
 
-    lenet = None
-    if rows == ROWS:                                       # every rank takes part (gradient all-reduce at N > 1)
+    lenet = vgg = None
+    if rows == ROWS and not args.no_extras:                # every rank takes part (gradient all-reduce at N > 1)
         try:
-            lenet = lenet_section(be, stream, rank, world)
+            lenet = cnn_section(be, stream, rank, world, "lenet")
+            vgg = cnn_section(be, stream, rank, world, "vgg", steps=5)
         except Exception as ex:                            # an extra: never lose the headline line over it
-            lenet = {"error": repr(ex)}
+            lenet = lenet or {"error": repr(ex)}
+            vgg = vgg or {"error": repr(ex)}
     if rank == 0:
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
@@ -453,8 +469,8 @@ def main():
             "roofline": roof(dom), "roofline_other": roof(oth),
             "checks": {"y_rows0_3_vs_f64": bool(ok_y), "g_rows0_3_bit_exact": bool(ok_g), "backend_error": err},
         }
-        line["extras"] = {"cfg4_lenet_train": lenet}
-        if world == 1 and rows == ROWS:
+        line["extras"] = {"cfg4_lenet_train": lenet, "cfg5_vgg_train": vgg}
+        if world == 1 and rows == ROWS and not args.no_extras:
             line["extras"]["cfg3_gemm_4096"] = gemm_section(be, stream, 4096)
         if not args.no_cpu_baseline and world == 1:
             sample_rows = 512

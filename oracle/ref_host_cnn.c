@@ -214,3 +214,137 @@ int drv_record_lenet(const char *path, u32 dry, u32 B, u32 steps, f32 lr, const 
     rec_close();
     return rc;
 }
+
+/* ------------------------------------------------------------------ config 5: VGG-style CNN */
+/* Three blocks of two [conv3x3 pad1 (no bias) + batchnorm(training) + relu] layers, a 2x2 max-pool after
+ * each block, flatten, linear, softmax cross-entropy, SGD.  chan[0..6] = input channels and the six conv
+ * widths (3,64,64,128,128,256,256 in the config); H = W = input size (64).  Batchnorm follows
+ * src/nn/batchnorm.c:7-112 (biased variance, eps 1e-5), staged: every [1,C,1,1] statistic is realised and
+ * x - mean is rebuilt per consumer; the running statistics, which the loss does not depend on, are not kept.
+ * params (flat): per conv layer W[Co,Ci,3,3], gamma[Co], beta[Co]; then Wl[F,classes], bl[classes]. */
+typedef struct { Term W, gamma, beta, xp, xhat, invstd, u, a; u32 Ci, Co, h; } VggLayer;
+
+static Term bc4(TinyHVM *ctx, Term stat_raw, u32 B, u32 C, u32 h) {       /* [1,C,1,1] statistic broadcast to [B,C,h,h] */
+    return thvm_expand(ctx, thvm_reshape(ctx, stat_raw, SHAPE(1, C, 1, 1)), SHAPE(B, C, h, h));
+}
+
+int drv_vgg(const char *dev, u32 B, u32 H, u32 classes, const u32 *chan, u32 steps, f32 lr, const f32 *x, const u8 *labels,
+            const f32 *params, u32 keep_grads) {
+    cpu_masked_leaf_workaround(dev);
+    TinyHVM *ctx = thvm_init(dev);
+    drv_ctx = ctx;
+    if (drv_after_init) drv_after_init();
+    lr = lr / (f32)drv_dp_world;
+    VggLayer L[6];
+    const f32 *p = params;
+    char nm[32];
+    for (u32 l = 0; l < 6; l++) {
+        u32 Ci = chan[l], Co = chan[l + 1];
+        L[l].Ci = Ci; L[l].Co = Co; L[l].h = H >> (l / 2);
+        snprintf(nm, sizeof nm, "W%u", l); rec_note(nm, 0);     L[l].W = thvm_tensor(ctx, p, SHAPE(Co, Ci, 3, 3)); p += (size_t)Co * Ci * 9;
+        snprintf(nm, sizeof nm, "gamma%u", l); rec_note(nm, 0); L[l].gamma = thvm_tensor(ctx, p, SHAPE(Co)); p += Co;
+        snprintf(nm, sizeof nm, "beta%u", l); rec_note(nm, 0);  L[l].beta = thvm_tensor(ctx, p, SHAPE(Co)); p += Co;
+    }
+    const u32 hf = H >> 3, F = chan[6] * hf * hf;
+    rec_note("Wl", 0); Term Wl = thvm_tensor(ctx, p, SHAPE(F, classes)); p += (size_t)F * classes;
+    rec_note("bl", 0); Term bl = thvm_tensor(ctx, p, SHAPE(classes)); p += classes;
+    u32 keep_id = ctx->tensor_count;
+    double t0 = now_s();
+    for (u32 s = 0; s < steps; s++) {
+        rec_mark("step_begin");
+        rec_note("x", 0);
+        Term act = thvm_tensor(ctx, x + (size_t)s * B * chan[0] * H * H, SHAPE(B, chan[0], H, H));
+        const u8 *lab = labels + (size_t)s * B;
+        Term pooled[3];
+        /* ---------------- forward ---------------- */
+        for (u32 l = 0; l < 6; l++) {
+            VggLayer *y = &L[l];
+            const u32 h = y->h, Co = y->Co;
+            const f32 inv = 1.0f / (f32)((u64)B * h * h);
+            y->xp = pad_hw(ctx, as4(ctx, act, B, y->Ci, h, h), 1);
+            Term z = conv_fwd(ctx, y->xp, y->W, term_era());                                             /* raw */
+            Term mean = realize(ctx, op2(ctx, UOP_MUL, sum023(ctx, as4(ctx, z, B, Co, h, h)), scalar(ctx, inv)));
+            Term d1 = op2(ctx, UOP_SUB, as4(ctx, z, B, Co, h, h), bc4(ctx, mean, B, Co, h));
+            Term d2 = op2(ctx, UOP_SUB, as4(ctx, z, B, Co, h, h), bc4(ctx, mean, B, Co, h));
+            Term var = realize(ctx, op2(ctx, UOP_MUL, sum023(ctx, op2(ctx, UOP_MUL, d1, d2)), scalar(ctx, inv)));
+            y->invstd = realize(ctx, op2(ctx, UOP_DIV, scalar(ctx, 1.f), op1(ctx, UOP_SQRT, op2(ctx, UOP_ADD, var, scalar(ctx, 1e-5f)))));
+            y->xhat = realize(ctx, op2(ctx, UOP_MUL, op2(ctx, UOP_SUB, as4(ctx, z, B, Co, h, h), bc4(ctx, mean, B, Co, h)), bc4(ctx, y->invstd, B, Co, h)));
+            y->u = realize(ctx, op2(ctx, UOP_ADD, op2(ctx, UOP_MUL, y->xhat, bc4(ctx, y->gamma, B, Co, h)), bc4(ctx, y->beta, B, Co, h)));
+            y->a = realize(ctx, op1(ctx, UOP_RELU, y->u));
+            act = y->a;
+            if (l & 1) { pooled[l / 2] = pool_fwd(ctx, y->a); act = pooled[l / 2]; }                     /* raw [B,Co,h/2,h/2,1,1] */
+        }
+        Term logits = linear_fwd(ctx, as2(ctx, act, B, F), Wl, bl, B, classes);
+        rec_note("onehot", 257);
+        Term loss = realize(ctx, cross_entropy_loss(ctx, logits, (u8 *)lab, B, classes));
+        /* ---------------- backward ---------------- */
+        Term dl = ce_backward(ctx, logits, lab, B, classes);
+        Term dWl = mm_raw(ctx, transpose2(ctx, as2(ctx, act, B, F)), dl);
+        Term dbl = realize(ctx, thvm_sum_axes(ctx, dl, (u32[]){0}, 1));
+        Term g = mm_raw(ctx, dl, transpose2(ctx, Wl));                                                   /* raw [B,1,F]: grad of the last pool */
+        Term dW[6], dgamma[6], dbeta[6];
+        for (i32 l = 5; l >= 0; l--) {
+            VggLayer *y = &L[l];
+            const u32 h = y->h, Co = y->Co, Ci = y->Ci;
+            const f32 N = (f32)((u64)B * h * h);
+            if (l & 1) g = pool_bwd(ctx, y->a, pooled[l / 2], g, B, Co, h / 2, h / 2);                   /* -> [B,Co,h,h] */
+            Term du = relu_bwd(ctx, as4(ctx, g, B, Co, h, h), y->u);
+            dbeta[l] = realize(ctx, sum023(ctx, du));
+            dgamma[l] = realize(ctx, sum023(ctx, op2(ctx, UOP_MUL, du, y->xhat)));
+            Term scale = op2(ctx, UOP_MUL, op2(ctx, UOP_MUL, bc4(ctx, y->gamma, B, Co, h), bc4(ctx, y->invstd, B, Co, h)), scalar(ctx, 1.0f / N));
+            Term inner = op2(ctx, UOP_SUB, op2(ctx, UOP_SUB, op2(ctx, UOP_MUL, du, scalar(ctx, N)), bc4(ctx, dbeta[l], B, Co, h)),
+                             op2(ctx, UOP_MUL, y->xhat, bc4(ctx, dgamma[l], B, Co, h)));
+            Term dz = realize(ctx, op2(ctx, UOP_MUL, scale, inner));
+            dW[l] = conv_wgrad(ctx, y->xp, dz, B, Ci, Co, h, h, 3);
+            if (l > 0) {
+                Term dxp = conv_dgrad(ctx, dz, y->W, Ci, Co, 3);                                         /* raw [B,Ci,h+2,h+2] */
+                u32 pairs[8] = {0, B, 0, Ci, 1, h + 1, 1, h + 1};
+                g = realize(ctx, op2(ctx, UOP_ADD, thvm_shrink(ctx, as4(ctx, dxp, B, Ci, h + 2, h + 2), pairs, 4), scalar(ctx, 0.f)));
+            }
+        }
+        { Term gr[20]; u32 n = 0; for (u32 l = 0; l < 6; l++) { gr[n++] = dW[l]; gr[n++] = dgamma[l]; gr[n++] = dbeta[l]; } gr[n++] = dWl; gr[n++] = dbl; dp_sum_grads(ctx, gr, n); }
+        rec_mark("read:loss");
+        keepf(ctx, "loss%u", s, loss);
+        if (s == 0 && keep_grads) {
+            keep(ctx, "logits", logits);
+            for (u32 l = 0; l < 6; l++) {
+                snprintf(nm, sizeof nm, "dW%u", l); keep(ctx, nm, dW[l]);
+                snprintf(nm, sizeof nm, "dgamma%u", l); keep(ctx, nm, dgamma[l]);
+                snprintf(nm, sizeof nm, "dbeta%u", l); keep(ctx, nm, dbeta[l]);
+            }
+            keep(ctx, "dWl", dWl); keep(ctx, "dbl", dbl);
+        }
+        /* ---------------- update ---------------- */
+        for (u32 l = 0; l < 6; l++) {
+            sgd(ctx, L[l].W, as4(ctx, dW[l], L[l].Co, L[l].Ci, 3, 3), lr);
+            sgd(ctx, L[l].gamma, as1(ctx, dgamma[l], L[l].Co), lr);
+            sgd(ctx, L[l].beta, as1(ctx, dbeta[l], L[l].Co), lr);
+        }
+        sgd(ctx, Wl, as2(ctx, dWl, F, classes), lr);
+        sgd(ctx, bl, as1(ctx, dbl, classes), lr);
+        rec_mark("read:bl");
+        f32 *sync = thvm_to_host(ctx, bl); (void)sync;
+        rec_mark("step_end");
+        if (s + 1 < steps) { thvm_reset(ctx, keep_id); thvm_sched_reset_runtime(); }
+    }
+    drv_secs = now_s() - t0;
+    for (u32 l = 0; l < 6; l++) {
+        snprintf(nm, sizeof nm, "W%u", l); keep(ctx, nm, L[l].W);
+        snprintf(nm, sizeof nm, "gamma%u", l); keep(ctx, nm, L[l].gamma);
+        snprintf(nm, sizeof nm, "beta%u", l); keep(ctx, nm, L[l].beta);
+    }
+    keep(ctx, "Wl", Wl); keep(ctx, "bl", bl);
+    drv_ctx = NULL;
+    thvm_free(ctx);
+    return 0;
+}
+
+int drv_record_vgg(const char *path, u32 dry, u32 B, u32 H, u32 classes, const u32 *chan, u32 steps, f32 lr, const f32 *x,
+                   const u8 *labels, const f32 *params) {
+    if (rec_open(path)) return 1;
+    drv_set_dp(1, rec_dp_hook, NULL);
+    int rc = drv_vgg(dry ? "record-dry" : "record", B, H, classes, chan, steps, lr, x, labels, params, 0);
+    drv_set_dp(1, NULL, NULL);
+    rec_close();
+    return rc;
+}

@@ -13,20 +13,10 @@ import pytest
 
 import hostref
 from tinyhvm_b200 import synth
+from tinyhvm_b200.configs import (LENET_NAMES, LENET_SHAPES, VGG_CHAN, lenet_inputs, vgg_inputs,  # noqa: F401
+                                   vgg_shapes)
 
 needs_ref = pytest.mark.skipif(not hostref.available(), reason="oracle/_ref/libthvm_host_ref.so not built")
-
-LENET_SHAPES = [(6, 1, 5, 5), (6,), (16, 6, 5, 5), (16,), (400, 120), (120,), (120, 84), (84,), (84, 10), (10,)]
-LENET_FAN_IN = [25, 25, 150, 150, 400, 400, 120, 120, 84, 84]
-LENET_NAMES = ["W1", "b1", "W2", "b2", "W3", "b3", "W4", "b4", "W5", "b5"]
-
-
-def lenet_inputs(B, steps, seed=synth.SEED_BASE + 4):
-    ps = [synth.kaiming_uniform(seed, 10 + i, int(np.prod(s)), f) for i, (s, f) in enumerate(zip(LENET_SHAPES, LENET_FAN_IN))]
-    x = synth.uniform(seed, 0, steps * B * 784)
-    lab = synth.labels(seed, 1, steps * B, 10)
-    return x, lab, ps
-
 
 def mlp_inputs(B=64, I=784, H=128, O=10, seed=synth.SEED_BASE + 1):
     x = synth.uniform(seed, 0, B * I)
@@ -108,6 +98,36 @@ def test_lenet_driver_matches_torch_autograd():
         assert np.allclose(r[n], q.detach().numpy().ravel(), atol=1e-6), n
 
 
+@needs_ref
+def test_vgg_driver_matches_torch_autograd():
+    import torch
+    F = torch.nn.functional
+    B, steps, lr, H, classes, chan = 4, 2, 0.05, 8, 10, (3, 4, 4, 8, 8, 8, 8)
+    x, lab, ps = vgg_inputs(B, steps, H, classes, chan)
+    shapes, names = vgg_shapes(chan, H, classes)
+    r = hostref.run("drv_vgg", "cpu", B, H, classes, np.array(chan, np.uint32), steps, lr, x, lab, np.concatenate(ps), 1)
+    tp = [torch.tensor(p.reshape(s), requires_grad=True) for p, s in zip(ps, shapes)]
+    for s in range(steps):
+        a = torch.tensor(x[s * B * 3 * H * H:(s + 1) * B * 3 * H * H].reshape(B, 3, H, H))
+        for l in range(6):
+            a = torch.relu(F.batch_norm(F.conv2d(a, tp[3 * l], padding=1), None, None, tp[3 * l + 1], tp[3 * l + 2], training=True, eps=1e-5))
+            if l & 1:
+                a = F.max_pool2d(a, 2)
+        loss = F.cross_entropy(a.reshape(B, -1) @ tp[18] + tp[19], torch.tensor(lab[s * B:(s + 1) * B].astype(np.int64)))
+        for q in tp:
+            q.grad = None
+        loss.backward()
+        assert abs(r[f"loss{s}"][0] - loss.item()) < 2e-5
+        if s == 0:
+            for n, q in zip(names, tp):
+                assert np.allclose(r["d" + n], q.grad.numpy().ravel(), atol=1e-5), n
+        with torch.no_grad():
+            for q in tp:
+                q -= lr * q.grad
+    for n, q in zip(names, tp):
+        assert np.allclose(r[n], q.detach().numpy().ravel(), atol=2e-6), n
+
+
 # ------------------------------------------------------------------ GPU: cuda == cpu through the reference's scheduler
 def compare_runs(driver, args, rtol, exact=()):
     cpu = hostref.run(driver, "cpu", *args)
@@ -152,3 +172,11 @@ def test_lenet_training_steps_cuda_vs_cpu():
     B, steps = 8, 2
     x, lab, ps = lenet_inputs(B, steps)
     compare_runs("drv_lenet", (B, steps, 0.01, x, lab, np.concatenate(ps), 1), 1e-4)
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_vgg_training_steps_cuda_vs_cpu():
+    B, steps, H, classes, chan = 8, 2, 16, 10, (3, 8, 8, 16, 16, 16, 16)
+    x, lab, ps = vgg_inputs(B, steps, H, classes, chan)
+    compare_runs("drv_vgg", (B, H, classes, np.array(chan, np.uint32), steps, 0.05, x, lab, np.concatenate(ps), 1), 2e-3)

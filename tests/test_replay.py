@@ -18,6 +18,7 @@ import pytest
 import hostref
 from test_host_dropin import LENET_NAMES, LENET_SHAPES, lenet_inputs, needs_ref
 from tinyhvm_b200 import replay
+from tinyhvm_b200.configs import onehot
 
 _u32, _u64, _vp = C.c_uint32, C.c_uint64, C.c_void_p
 
@@ -49,12 +50,6 @@ class RefTarget:
                                         C.byref(a.red) if a.has_red else None, a.dts, _u32(a.out_dt))
 
 
-def onehot(labels, classes=10):
-    o = np.zeros((labels.size, classes), dtype=np.float32)
-    o[np.arange(labels.size), labels] = 1.0
-    return o.ravel()
-
-
 def record(tmp_path, B, steps, dry=0):
     x, lab, ps = lenet_inputs(B, steps)
     path = tmp_path / f"lenet_b{B}.thtr"
@@ -68,7 +63,7 @@ def replay_lenet(target, recs, B, steps, data, lr=0.01):
     rp.run_prefix(dict(zip(LENET_NAMES, ps)))
     losses = []
     for s in range(steps):
-        ext = {"x": x[s * B * 784:(s + 1) * B * 784], "onehot": onehot(lab[s * B:(s + 1) * B]),
+        ext = {"x": x[s * B * 784:(s + 1) * B * 784], "onehot": onehot(lab[s * B:(s + 1) * B], 10),
                "lr": np.array([lr], dtype=np.float32)}
         cyc = rp.cycles[min(s, 1)]                        # cycle 0 = first step, cycle 1 = every later step
         out = rp.run(cyc, ext)
@@ -123,5 +118,80 @@ def test_replay_on_gpu_matches_recorded_run(tmp_path, cuda):
         assert abs(losses[s] - float(res[f"loss{s}"][0])) < 2e-5, s
     for n in LENET_NAMES:
         assert np.allclose(params[n], res[n], rtol=1e-4, atol=1e-6), n
+    cuda.reset(0)
+    assert cuda.last_error() == ""
+
+
+# ------------------------------------------------------------------ the VGG-style step (conv3x3 + batchnorm + relu blocks)
+VGG_SMALL = dict(B=8, H=8, classes=10, chan=(3, 4, 4, 8, 8, 8, 8))
+
+
+def record_vgg(tmp_path, steps, dry=0):
+    from tinyhvm_b200.configs import vgg_inputs
+    c = VGG_SMALL
+    x, lab, ps = vgg_inputs(c["B"], steps, c["H"], c["classes"], c["chan"])
+    path = tmp_path / "vgg_small.thtr"
+    res = hostref.run("drv_record_vgg", str(path), dry, c["B"], c["H"], c["classes"], np.array(c["chan"], np.uint32), steps, 0.05,
+                      x, lab, np.concatenate(ps))
+    return path, res, (x, lab, ps)
+
+
+def replay_vgg(target, recs, steps, data, lr=0.05):
+    from tinyhvm_b200.configs import vgg_shapes
+    c = VGG_SMALL
+    x, lab, ps = data
+    shapes, names = vgg_shapes(c["chan"], c["H"], c["classes"])
+    rp = replay.Replayer(target, recs)
+    rp.run_prefix(dict(zip(names, ps)))
+    losses, n = [], c["B"] * 3 * c["H"] * c["H"]
+    for s in range(steps):
+        ext = {"x": x[s * n:(s + 1) * n], "onehot": onehot(lab[s * c["B"]:(s + 1) * c["B"]], c["classes"]),
+               "lr": np.array([lr], dtype=np.float32)}
+        losses.append(float(rp.run(rp.cycles[min(s, 1)], ext)["loss"][0]))
+    params = {}
+    for k, (name, shape) in enumerate(zip(names, shapes)):
+        buf = np.empty(int(np.prod(shape)), dtype=np.float32)
+        target.read(k + 1, buf.ctypes.data, buf.nbytes)
+        params[name] = buf
+    return losses, params
+
+
+@needs_ref
+def test_vgg_replay_through_reference_cpu_backend_is_bit_exact(tmp_path, ref):
+    steps = 4
+    path, res, data = record_vgg(tmp_path, steps)
+    recs = replay.load_trace(path)
+    prefix, cycles = replay.split_steps(recs)
+    key = lambda c: [(r.op, r.f, r.blob) for r in c if r.op != replay.MARK]
+    assert key(cycles[1]) == key(cycles[2]), "the steady-state step cycle changes from step to step"
+    losses, params = replay_vgg(RefTarget(ref), recs, steps, data)
+    for s in range(steps):
+        assert losses[s] == float(res[f"loss{s}"][0]), s
+    for n in params:
+        assert np.array_equal(params[n], res[n]), n
+    ref.lib.ref_pool_reset(_u32(0))
+
+
+def test_committed_vgg_trace_parses():
+    recs = replay.load_trace(replay.TRACE_DIR / "vgg_b512.thtr.gz")
+    prefix, cycles = replay.split_steps(recs)
+    assert len(cycles) >= 2
+    assert 120 <= sum(1 for r in cycles[1] if r.op == replay.DISPATCH) <= 200
+    ext = {(r.f[3], r.f[2]) for r in cycles[1] if r.op == replay.WRITE and r.f[1]}
+    assert ext == {("x", 512 * 3 * 64 * 64 * 4), ("onehot", 512 * 100 * 4), ("lr", 4)}, ext
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_vgg_replay_on_gpu_matches_recorded_run(tmp_path, cuda):
+    steps = 3
+    path, res, data = record_vgg(tmp_path, steps)
+    recs = replay.load_trace(path)
+    cuda.reset(0)
+    losses, params = replay_vgg(replay.CudaTarget(cuda), recs, steps, data)
+    for s in range(steps):
+        assert abs(losses[s] - float(res[f"loss{s}"][0])) < 1e-4, s
+    for n in params:
+        assert np.allclose(params[n], res[n], rtol=2e-3, atol=2e-5), n
     cuda.reset(0)
     assert cuda.last_error() == ""

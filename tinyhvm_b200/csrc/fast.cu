@@ -268,6 +268,115 @@ __global__ void __launch_bounds__(256) k_red_inner(const __grid_constant__ FDesc
     }
 }
 
+// ------------------------------------------------------------------ streamlined forms: every leaf flat or a single element
+// When every leaf is laid out exactly like the iteration space (or is one broadcast
+// element) no coordinates are needed at all: the loads of a trip are issued back to
+// back, branch-free, from per-leaf base pointers.  These forms carry the big
+// contiguous chains (y = sum_last(relu(a*b+c)) and its VJP) at the HBM rate.
+template <class EV>
+struct FlatLeaves {
+    static constexpr int NL = EV::MAXL;
+    const float4 *p[NL];
+    float sc[NL];
+    bool fl[NL];
+    __device__ __forceinline__ void init(const FDesc &D) {
+        const int nl = EV::nleaves(D.prog);
+#pragma unroll
+        for (int i = 0; i < NL; i++) {
+            fl[i] = false; sc[i] = 0.0f; p[i] = nullptr;
+            if (i < nl) {
+                const FLeaf &L = D.leaf[i];
+                fl[i] = L.mode == 1;
+                if (fl[i]) p[i] = reinterpret_cast<const float4 *>(L.ptr + L.off);
+                else sc[i] = L.ptr[L.off];
+            }
+        }
+    }
+    // the chain's result for the 4 elements of vector `idx`
+    __device__ __forceinline__ float4 eval(const FDesc &D, unsigned long long idx) const {
+        float v[EV::NV][4];
+#pragma unroll
+        for (int i = 0; i < NL; i++) {
+            float4 q = make_float4(sc[i], sc[i], sc[i], sc[i]);
+            if (fl[i]) q = __ldg(p[i] + idx);
+            v[i][0] = q.x; v[i][1] = q.y; v[i][2] = q.z; v[i][3] = q.w;
+        }
+        EV::template run<4>(D.prog, v);
+        const int r = EV::result(D.prog);
+        return make_float4(v[r][0], v[r][1], v[r][2], v[r][3]);
+    }
+};
+template <class EV> constexpr int flat_unroll() { return EV::MAXL <= 4 ? 2 : 1; }
+
+// out[o] = reduce over one contiguous row of n_red elements; G = 256: one CTA per row, G = 32: one warp per row
+template <class EV, int G>
+__global__ void __launch_bounds__(256) k_rows(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    constexpr int U = flat_unroll<EV>();
+    __shared__ float part[8];
+    FlatLeaves<EV> LV;
+    LV.init(D);
+    const unsigned rtype = D.rtype;
+    const unsigned cols4 = (unsigned)(D.n_red / 4);
+    const unsigned lane = threadIdx.x % G;
+    const unsigned long long per_cta = 256 / G;
+    for (unsigned long long row = (unsigned long long)blockIdx.x * per_cta + threadIdx.x / G; row < D.n_out;
+         row += (unsigned long long)gridDim.x * per_cta) {
+        const unsigned long long base = row * cols4;
+        float acc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) acc[u] = red_init(rtype);
+        unsigned i = lane;
+        for (; i + (U - 1) * G < cols4; i += U * G) {
+            float4 r[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) r[u] = LV.eval(D, base + i + u * G);
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                acc[u] = red_combine(rtype, acc[u], red_combine(rtype, red_combine(rtype, r[u].x, r[u].y), red_combine(rtype, r[u].z, r[u].w)));
+        }
+        for (; i < cols4; i += G) {
+            const float4 r = LV.eval(D, base + i);
+            acc[0] = red_combine(rtype, acc[0], red_combine(rtype, red_combine(rtype, r.x, r.y), red_combine(rtype, r.z, r.w)));
+        }
+        float a = acc[0];
+#pragma unroll
+        for (int u = 1; u < U; u++) a = red_combine(rtype, a, acc[u]);
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1) a = red_combine(rtype, a, __shfl_down_sync(0xffffffffu, a, w));
+        if (G == 256) {                       // rows are uniform per CTA here, so the barriers are too
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = a;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                a = part[0];
+                for (int w = 1; w < 8; w++) a = red_combine(rtype, a, part[w]);
+                out[row] = a;
+            }
+        } else if (lane == 0) {
+            out[row] = a;
+        }
+    }
+}
+
+// out = chain(leaves) over one flat run of numel elements; each CTA takes a contiguous slab
+template <class EV>
+__global__ void __launch_bounds__(256) k_ew_flat(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    constexpr int U = flat_unroll<EV>();
+    FlatLeaves<EV> LV;
+    LV.init(D);
+    const unsigned long long n4 = D.numel / 4;
+    float4 *o4 = reinterpret_cast<float4 *>(out);
+    for (unsigned long long i = (unsigned long long)blockIdx.x * (256 * U) + threadIdx.x; i < n4; i += (unsigned long long)gridDim.x * (256 * U)) {
+        float4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (i + u * 256 < n4) r[u] = LV.eval(D, i + u * 256);
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (i + u * 256 < n4) o4[i + u * 256] = r[u];
+    }
+}
+
 // ------------------------------------------------------------------ reduce, innermost dim kept
 template <class EV>
 __global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc D, float *__restrict__ out) {
@@ -319,7 +428,9 @@ struct FastDesc {
     int   strategy;                 // 0 ew, 1 reduce-inner, 2 reduce-outer
     int   group;                    // threads per output for reduce-inner
     long long min_off[FL], max_off[FL];
-    const char *name;
+    const char *name, *flat_name;   // kernel family for the launch statistics: general form, streamlined form
+    bool  flat_shape;               // every leaf flat or one element, shape fit for the streamlined kernels
+    bool  flat;                     // decided per launch: flat_shape and all pointers 16-byte aligned
 };
 
 static bool build_fast(const GenDesc &H, FastDesc &F) {
@@ -442,7 +553,12 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
 
     // strategy
     const unsigned sms = (unsigned)g.sm_count;
-    if (!H.has_reduce) { F.strategy = 0; F.name = D.chain ? (D.vec == 4 ? "ew_vec4_static" : "ew_scalar_static") : (D.vec == 4 ? "ew_vec4_interp" : "ew_scalar_interp"); return true; }
+    bool all_flat = D.vec == 4;                    // every leaf flat (and 16-byte loadable) or one element
+    for (unsigned i = 0; i < H.n_leaves; i++)
+        if (!(D.leaf[i].mode == 2 || (D.leaf[i].mode == 1 && D.leaf[i].vec))) all_flat = false;
+    F.flat_shape = false; F.flat = false;
+    F.flat_name = "";
+    if (!H.has_reduce) { F.strategy = 0; F.flat_shape = all_flat; F.flat_name = D.chain ? "ew_flat_static" : "ew_flat_interp"; F.name = D.chain ? (D.vec == 4 ? "ew_vec4_static" : "ew_scalar_static") : (D.vec == 4 ? "ew_vec4_interp" : "ew_scalar_interp"); return true; }
     if (D.is_red[in]) {
         F.strategy = 1;
         const unsigned long long items = D.n_red / D.vec;
@@ -454,6 +570,13 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
             unsigned long long most = items / 1024;                 // keep >= 4 vectors per thread per slice
             if (want > most) want = most;
             if (want > 1) D.split = (unsigned)want;
+        }
+        if (all_flat && D.n_r == 1 && D.split == 1 && items >= 32 && items <= 0x7FFFFFFFull) {
+            // contiguous rows: a CTA per row streams best once a row gives every thread two vectors
+            F.flat_shape = true;
+            if (items >= 512 && D.n_out >= 2ull * sms) F.group = 256;
+            F.flat_shape = F.group != 1;
+            F.flat_name = F.group == 256 ? "reduce_rows_cta" : "reduce_rows_warp";
         }
         F.name = F.group == 256 ? (D.split > 1 ? "reduce_inner_cta_split" : "reduce_inner_cta") : (F.group == 32 ? "reduce_inner_warp" : "reduce_inner_thread");
         return true;
@@ -483,6 +606,16 @@ void free_fast(Plan *p) { delete (FastDesc *)p->fast; p->fast = nullptr; free_co
 template <class EV>
 static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
     const unsigned long long items = D.numel / D.vec;
+    if (F.flat && F.strategy == 0) {
+        const unsigned long long ctas = (items + 256 * flat_unroll<EV>() - 1) / (256 * flat_unroll<EV>());
+        k_ew_flat<EV><<<(unsigned)(ctas < 0x7FFFFFFFull ? ctas : 0x7FFFFFFFull), 256, 0, g.stream>>>(D, out);
+        return;
+    }
+    if (F.flat && F.strategy == 1) {
+        if (F.group == 256) k_rows<EV, 256><<<(unsigned)(D.n_out < 0x7FFFFFFFull ? D.n_out : 0x7FFFFFFFull), 256, 0, g.stream>>>(D, out);
+        else                k_rows<EV, 32><<<grid_for(D.n_out, 8, 8), 256, 0, g.stream>>>(D, out);
+        return;
+    }
     if (F.strategy == 0) {
         const unsigned grid = grid_for(items, 256, 8);
         if (D.vec == 4) k_ew<EV, 4><<<grid, 256, 0, g.stream>>>(D, out);
@@ -524,6 +657,9 @@ bool launch_fast(Plan *p, const GenArgs &args) {
     }
     float *out = (float *)args.out;
     if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return false;
+    F.flat = F.flat_shape;
+    for (unsigned i = 0; i < D.prog.n_leaves; i++)
+        if (D.leaf[i].mode == 1 && !D.leaf[i].vec) F.flat = false;
     if (g.profile_level >= 2) {
         int w = snprintf(g.last_shape, sizeof g.last_shape, "dims=[");
         for (unsigned d = 0; d < D.rank; d++) w += snprintf(g.last_shape + w, sizeof g.last_shape - w, "%u%s%s", D.dims[d], D.is_red[d] ? "r" : "", d + 1 < D.rank ? "," : "");
@@ -545,7 +681,7 @@ bool launch_fast(Plan *p, const GenArgs &args) {
         case 8: launch_with<StaticEval<8>>(F, D, out); break;
         default: launch_with<InterpEval>(F, D, out); break;
     }
-    after_launch(F.name);
+    after_launch(F.flat ? F.flat_name : F.name);
     if (F.strategy != 0 && D.split > 1) {
         k_red_final<<<grid_for(D.n_out, 256, 4), 256, 0, g.stream>>>((const float *)g.scratch, out, D.n_out, D.split, D.rtype);
         after_launch("reduce_final");

@@ -214,19 +214,19 @@ void thvm_cuda_dispatch_kernel_rs(uint32_t out_buf, uint32_t *leaf_bufs, const t
         (*cache)[key] = p;
     }
 
-    Buf &ob = buf_checked(out_buf, "dispatch(out)");
     GenArgs args;
-    args.out = ob.ptr;
-    args.out_cap = ob.bytes / dtype_bytes(p->host.out_dtype);
     for (uint32_t i = 0; i < n_leaves; i++) {
         Buf &lb = buf_checked(leaf_bufs[i], "dispatch(leaf)");
         args.leaf[i] = lb.ptr;
         args.cap[i] = lb.bytes / dtype_bytes(p->host.leaves[i].dtype);
     }
+    uint64_t need_out = p->host.has_reduce ? p->host.out_numel : p->host.full_numel;
+    Buf &ob = buf_for_output(out_buf, "dispatch(out)", need_out * dtype_bytes(p->host.out_dtype));   // after the leaves: out may alias one
+    args.out = ob.ptr;
+    args.out_cap = ob.bytes / dtype_bytes(p->host.out_dtype);
     args.status = g.dev_status;
     mark_device_written(out_buf);
 
-    uint64_t need_out = p->host.has_reduce ? p->host.out_numel : p->host.full_numel;
     if (need_out > args.out_cap) {
         set_error("dispatch: output buffer %u holds %llu elements, kernel writes %llu", out_buf,
                   (unsigned long long)args.out_cap, (unsigned long long)need_out);

@@ -70,7 +70,17 @@ Buf &buf_checked(uint32_t id, const char *who) {
             THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.stream));
         }
     }
+    if (b.zero_pending) {
+        THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
+        b.zero_pending = false;
+    }
     return b;
+}
+
+Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written) {
+    Buf &b = buf_live(id, who);
+    if (b.ptr && b.zero_pending && bytes_written >= b.bytes) b.zero_pending = false;
+    return buf_checked(id, who);
 }
 
 void *scratch_reserve(uint64_t bytes) {
@@ -239,11 +249,11 @@ uint32_t thvm_cuda_buf_alloc(uint64_t bytes) {
             set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
             return 0;
         }
-        THC_CUDA_OK(cudaMemsetAsync(p, 0, sz, g.stream));
     }
     uint32_t id = g.count++;
     Buf &b = g.bufs[id];
     b.live = true; b.ptr = p; b.bytes = bytes; b.refcount = 1;
+    b.zero_pending = p != nullptr;                 // the zero-fill is issued on first use, and dropped if that use overwrites everything
     if (bytes <= SHADOW_MAX) {
         b.shadow = (uint8_t *)calloc(1, SHADOW_MAX);
         b.shadow_valid = true;                     // zeros, like a fresh device buffer
@@ -283,6 +293,10 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
     if (bytes == 0) return;
     if (b.shadow) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
     if (!b.ptr) return;                            // host-only buffer: uploaded if and when the device needs it
+    if (b.zero_pending) {
+        if (bytes < b.bytes) THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
+        b.zero_pending = false;
+    }
     if (bytes <= RING_MAX_MSG) {
         uint8_t *stage = ring_take(bytes);
         memcpy(stage, data, bytes);
@@ -302,7 +316,7 @@ static void read_impl(uint32_t id, void *out, uint64_t bytes, bool sync) {
     if (bytes > n) memset((uint8_t *)out + n, 0, bytes - n);   // past the end reads as zero (src/backend/metal/pool.m:214-218)
     if (n == 0) return;
     if (b.shadow && b.shadow_valid) { memcpy(out, b.shadow, n); return; }
-    if (!b.ptr) { memset(out, 0, n); return; }
+    if (!b.ptr || b.zero_pending) { memset(out, 0, n); return; }
     THC_CUDA_OK(cudaMemcpyAsync(out, b.ptr, n, cudaMemcpyDeviceToHost, g.stream));
     if (sync) check_device_status("buf_read");                // drains the stream
 }
@@ -318,8 +332,8 @@ void thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes) {
         memcpy(dl.shadow, sl.shadow, nbytes); dl.shadow_valid = true;      // both still host-only
         return;
     }
-    Buf &d = buf_checked(dst_buf, "buf_copy(dst)");
     Buf &s = buf_checked(src_buf, "buf_copy(src)");
+    Buf &d = buf_for_output(dst_buf, "buf_copy(dst)", nbytes);
     uint64_t n = nbytes;
     if (n > d.bytes || n > s.bytes) {
         set_error("buf_copy: %llu bytes exceed dst %llu / src %llu", (unsigned long long)n,

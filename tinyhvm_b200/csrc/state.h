@@ -20,6 +20,7 @@ struct Buf {
     uint32_t refcount = 0;
     uint8_t *shadow   = nullptr;   // host copy of a small host-written buffer
     bool     shadow_valid = false; // false once a kernel or copy wrote the buffer
+    bool     zero_pending = false; // fresh device memory whose zero-fill has not been issued yet
 };
 
 struct State {
@@ -69,6 +70,9 @@ void set_error(const char *fmt, ...);
 
 // a live buffer with device memory behind it (materialised on demand), or a fatal error
 Buf &buf_checked(uint32_t id, const char *who);
+// the output buffer of a launch that overwrites its first `bytes_written` bytes: the zero-fill a fresh
+// buffer owes is dropped when that covers the whole buffer.  Resolve the inputs of the launch first.
+Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written);
 // a live buffer that may still be host-only
 Buf &buf_live(uint32_t id, const char *who);
 // scratch of at least `bytes` (stream-ordered reuse: all users run on g.stream)
