@@ -235,6 +235,19 @@ int      thvm_cuda_dp_rank(void);
 int      thvm_cuda_dp_allreduce_sum(const uint32_t *buf_ids, const uint64_t *counts, uint32_t n_bufs);
 void     thvm_cuda_dp_shutdown(void);
 
+/* ---- index-producing kernels (integer outputs, bit-exact) ----
+ * 2x2 stride-2 max-pool of `planes` contiguous [H, W] f32 planes: values to `out_val`
+ * ([planes, H/2, W/2] f32) and, when `out_idx` != 0, the position of the winner inside
+ * its window as u8 0..3 in scan order (0,0),(0,1),(1,0),(1,1); strict '>' so the first
+ * maximum wins.  Replaces the arithmetic of the reference's max-pool shader
+ * (src/shaders.metal:427-458); the value half equals what the RMAX dispatch of
+ * thvm_maxpool2d (src/nn/conv.c:484-513) produces.  0 = launched, 1 = bad argument. */
+int      thvm_cuda_maxpool2x2_index(uint32_t out_val, uint32_t out_idx, uint32_t x, uint32_t planes, uint32_t H, uint32_t W);
+/* Per-row argmax of a contiguous [rows, cols] f32 buffer into u32[rows]: the first index
+ * whose value is strictly greater than every earlier one.  Replaces the host loop of
+ * thvm_argmax (src/ops/_.c:502-524), which reads the whole tensor back first. */
+int      thvm_cuda_argmax_rows(uint32_t out_u32, uint32_t x, uint32_t rows, uint32_t cols);
+
 /* ---- allocation-free variant (no counterpart in the reference) ----
  * out[c] = sum over b and i of x[b][c][i] for a contiguous f32 tensor x[B][C][HW]
  * (the batch-norm channel statistic), computed by the same split reduce kernels

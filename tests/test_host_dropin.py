@@ -180,3 +180,22 @@ def test_vgg_training_steps_cuda_vs_cpu():
     B, steps, H, classes, chan = 8, 2, 16, 10, (3, 8, 8, 16, 16, 16, 16)
     x, lab, ps = vgg_inputs(B, steps, H, classes, chan)
     compare_runs("drv_vgg", (B, H, classes, np.array(chan, np.uint32), steps, 0.05, x, lab, np.concatenate(ps), 1), 2e-3)
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_lowered_kop_programs_cuda_vs_cpu(monkeypatch):
+    """With THVM_CUDA_UOP set the hub fills the dispatch_uop_kernel slot, so the reference's scheduler hands
+    over the lowered KOP programs of its own lowerer (src/lower/_.c:765-973, src/schedule/_.c:2370) and the
+    device-side KOP interpreter runs them: same tensors as the CPU run of the same programs."""
+    import tinyhvm_b200
+    monkeypatch.setenv("THVM_CUDA_UOP", "1")
+    R, C = 64, 1024
+    a, b, c = (synth.normal(synth.SEED_BASE + 2, t, R * C) for t in range(3))
+    compare_runs("drv_chain", (R, C, a, b, c), 1e-5, exact=("g",))
+    last = tinyhvm_b200.load().thvm_cuda_last_plan()
+    assert last == b"uop_program", f"the KOP interpreter did not run (last kernel family: {last})"
+    n = 48
+    A, B = (synth.normal(synth.SEED_BASE + 3, t, n * n) / np.float32(np.sqrt(n)) for t in range(2))
+    compare_runs("drv_gemm", (n, A, B), 1e-4)
+    compare_runs("drv_mlp", mlp_inputs(B=16, I=64, H=32), 1e-4)

@@ -70,6 +70,8 @@ SYMBOLS = {
     "thvm_cuda_dp_rank": (C.c_int, []),
     "thvm_cuda_dp_allreduce_sum": (C.c_int, [C.POINTER(_u32), C.POINTER(_u64), _u32]),
     "thvm_cuda_dp_shutdown": (None, []),
+    "thvm_cuda_maxpool2x2_index": (C.c_int, [_u32, _u32, _u32, _u32, _u32, _u32]),
+    "thvm_cuda_argmax_rows": (C.c_int, [_u32, _u32, _u32, _u32]),
     "thvm_cuda_channel_sums_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _vp]),
     "thvm_cuda_signature": (_u64, [C.POINTER(abi.FusedOp), _u32, C.POINTER(_PV), _vp, _u32,
                                    C.POINTER(abi.Shape), C.POINTER(abi.ReduceSpec)]),

@@ -68,11 +68,6 @@ static int cuda_hub_init(void) {
         b->op_mm               = cuda_hub_sym("thvm_cuda_op_mm");
         b->op_reduce           = cuda_hub_sym("thvm_cuda_op_reduce");
         b->dispatch_kernel_rs  = cuda_hub_sym("thvm_cuda_dispatch_kernel_rs");
-        // The scheduler prefers the lowered KOP form whenever this slot is set
-        // (src/schedule/_.c:2370).  The structured form carries the views and
-        // the reduce spec the kernel selection needs, so the slot stays NULL
-        // unless THVM_CUDA_UOP=1 asks for the KOP interpreter.
-        b->dispatch_uop_kernel = getenv("THVM_CUDA_UOP") ? cuda_hub_sym("thvm_cuda_dispatch_uop_kernel") : NULL;
         b->contiguify          = cuda_hub_sym("thvm_cuda_contiguify");
         b->buf_copy            = cuda_hub_sym("thvm_cuda_buf_copy");
         b->buf_read_nosync     = cuda_hub_sym("thvm_cuda_buf_read_nosync");
@@ -84,6 +79,11 @@ static int cuda_hub_init(void) {
         b->profile_report      = cuda_hub_sym("thvm_cuda_profile_report");
         b->profile_reset       = cuda_hub_sym("thvm_cuda_profile_reset");
     }
+    // The scheduler prefers the lowered KOP form whenever this slot is set
+    // (src/schedule/_.c:2370).  The structured form carries the views and the
+    // reduce spec the kernel selection needs, so the slot stays NULL unless
+    // THVM_CUDA_UOP=1 asks for the KOP interpreter (looked at on every init).
+    cuda_backend.dispatch_uop_kernel = getenv("THVM_CUDA_UOP") ? cuda_hub_sym("thvm_cuda_dispatch_uop_kernel") : NULL;
     int (*lib_init)(void) = cuda_hub_sym("thvm_cuda_init");
     return lib_init();
 }

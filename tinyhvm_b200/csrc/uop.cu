@@ -122,6 +122,73 @@ __global__ void __launch_bounds__(256) k_adam(float *__restrict__ p, const float
     }
 }
 
+// 2x2 stride-2 max-pool that also records which element of the window won: scan order
+// (0,0),(0,1),(1,0),(1,1), strict '>' so the first maximum wins, index stored as u8 0..3
+// (the arithmetic of the reference's max-pool shader, src/shaders.metal:427-458).
+// One thread per pair of neighbouring outputs: two 16-byte loads (one per input row).
+__global__ void __launch_bounds__(256) k_maxpool2x2_index(const float *__restrict__ x, float *__restrict__ y, uint8_t *__restrict__ idx,
+                                                          unsigned long long planes, unsigned H, unsigned W, unsigned vec) {
+    const unsigned OH = H / 2, OW = W / 2;
+    const unsigned per_row = vec ? OW / 2 : OW;                      // work items per output row
+    const unsigned long long items = planes * OH * per_row;
+    for (unsigned long long it = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; it < items;
+         it += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned c = (unsigned)(it % per_row);
+        const unsigned long long rowi = it / per_row;                // plane * OH + oy
+        const unsigned oy = (unsigned)(rowi % OH);
+        const unsigned long long plane = rowi / OH;
+        const float *r0 = x + (plane * H + 2ull * oy) * W;
+        const float *r1 = r0 + W;
+        const unsigned long long o = rowi * OW;
+        if (vec) {
+            const float4 a = *reinterpret_cast<const float4 *>(r0 + 4u * c), b = *reinterpret_cast<const float4 *>(r1 + 4u * c);
+            float b0 = a.x; uint8_t i0 = 0;
+            if (a.y > b0) { b0 = a.y; i0 = 1; }
+            if (b.x > b0) { b0 = b.x; i0 = 2; }
+            if (b.y > b0) { b0 = b.y; i0 = 3; }
+            float b1 = a.z; uint8_t i1 = 0;
+            if (a.w > b1) { b1 = a.w; i1 = 1; }
+            if (b.z > b1) { b1 = b.z; i1 = 2; }
+            if (b.w > b1) { b1 = b.w; i1 = 3; }
+            *reinterpret_cast<float2 *>(y + o + 2u * c) = make_float2(b0, b1);
+            if (idx) { idx[o + 2u * c] = i0; idx[o + 2u * c + 1] = i1; }
+        } else {
+            const float w0 = r0[2u * c], w1 = r0[2u * c + 1], w2 = r1[2u * c], w3 = r1[2u * c + 1];
+            float best = w0; uint8_t bi = 0;
+            if (w1 > best) { best = w1; bi = 1; }
+            if (w2 > best) { best = w2; bi = 2; }
+            if (w3 > best) { best = w3; bi = 3; }
+            y[o + c] = best;
+            if (idx) idx[o + c] = bi;
+        }
+    }
+}
+
+// first index of the row maximum (strictly greater wins, so ties keep the earlier index): one warp per row.
+// The reference computes this on the host after a full read-back (src/ops/_.c:502-524).
+__global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x, uint32_t *__restrict__ out, unsigned rows, unsigned cols) {
+    const unsigned lane = threadIdx.x & 31;
+    for (unsigned long long r = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows;
+         r += ((unsigned long long)gridDim.x * blockDim.x) >> 5) {
+        const float *row = x + r * cols;
+        // per-lane candidate over its strided columns, seeded like the host loop: best = column 0
+        float bv = row[0]; unsigned bi = 0;
+        for (unsigned c = lane; c < cols; c += 32) {
+            const float v = row[c];
+            if (c != 0 && (v > bv)) { bv = v; bi = c; }
+        }
+        // a candidate replaces another only if strictly greater, or equal with a smaller index;
+        // a NaN never wins a '>' test, exactly as in the sequential scan
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1) {
+            const float ov = __shfl_down_sync(0xffffffffu, bv, w);
+            const unsigned oi = __shfl_down_sync(0xffffffffu, bi, w);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[r] = bi;
+    }
+}
+
 }  // namespace thc
 
 using namespace thc;
@@ -183,6 +250,36 @@ void thvm_cuda_adam_step(uint32_t param, uint32_t grad, uint32_t m, uint32_t v, 
     k_adam<<<grid_for(n, 256, 8), 256, 0, g.stream>>>((float *)bp.ptr, (const float *)bg.ptr, (float *)bm.ptr,
                                                       (float *)bv.ptr, lr, beta1, beta2, eps, bc1, bc2, n);
     after_launch("adam_step");
+}
+
+int thvm_cuda_maxpool2x2_index(uint32_t out_val, uint32_t out_idx, uint32_t x, uint32_t planes, uint32_t H, uint32_t W) {
+    if (H < 2 || W < 2 || planes == 0) { set_error("maxpool2x2_index: empty shape"); return 1; }
+    const uint64_t in_n = (uint64_t)planes * H * W, out_n = (uint64_t)planes * (H / 2) * (W / 2);
+    Buf &bx = buf_checked(x, "maxpool2x2_index(x)");
+    Buf &by = buf_for_output(out_val, "maxpool2x2_index(y)", out_n * 4);
+    Buf *bi = out_idx ? &buf_for_output(out_idx, "maxpool2x2_index(idx)", out_n) : nullptr;
+    if (bx.bytes < in_n * 4 || by.bytes < out_n * 4 || (bi && bi->bytes < out_n)) { set_error("maxpool2x2_index: a buffer is too small"); return 1; }
+    mark_device_written(out_val);
+    if (out_idx) mark_device_written(out_idx);
+    const unsigned vec = (W % 4 == 0) ? 1u : 0u;                   // rows start 16-byte aligned, outputs 8-byte aligned
+    const uint64_t items = (uint64_t)planes * (H / 2) * (vec ? W / 4 : W / 2);
+    profile_begin();
+    k_maxpool2x2_index<<<grid_for(items, 256, 8), 256, 0, g.stream>>>((const float *)bx.ptr, (float *)by.ptr, bi ? (uint8_t *)bi->ptr : nullptr,
+                                                                     planes, H, W, vec);
+    after_launch("maxpool2x2_index");
+    return 0;
+}
+
+int thvm_cuda_argmax_rows(uint32_t out_u32, uint32_t x, uint32_t rows, uint32_t cols) {
+    if (rows == 0 || cols == 0) { set_error("argmax_rows: empty shape"); return 1; }
+    Buf &bx = buf_checked(x, "argmax_rows(x)");
+    Buf &bo = buf_for_output(out_u32, "argmax_rows(out)", (uint64_t)rows * 4);
+    if (bx.bytes < (uint64_t)rows * cols * 4 || bo.bytes < (uint64_t)rows * 4) { set_error("argmax_rows: a buffer is too small"); return 1; }
+    mark_device_written(out_u32);
+    profile_begin();
+    k_argmax_rows<<<grid_for(rows, 8, 8), 256, 0, g.stream>>>((const float *)bx.ptr, (uint32_t *)bo.ptr, rows, cols);
+    after_launch("argmax_rows");
+    return 0;
 }
 
 }  // extern "C"
