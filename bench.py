@@ -144,7 +144,7 @@ def dp_setup(be, rank: int, world: int):
     _dp_ready = True
 
 
-def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: int = 10):
+def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: int = 10, use_graph: bool = True):
     """SGD steps of a CNN config at a fixed global batch, batch-sharded over the ranks: every rank replays the
     recorded step program of its shard size (tinyhvm_b200/traces, the vtable calls the reference's
     scheduler makes for the staged step) against the C ABI; gradients are summed with
@@ -181,6 +181,17 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     if world > 1:
         dist.barrier()
     be.sync(); torch.cuda.synchronize()
+    graph = None
+    if use_graph:                                          # the steady-state step as one CUDA graph launch
+        graph = rp.capture(rp.cycles[1], {"x": xs[0].numpy(), "onehot": ohs[0].numpy(), "lr": lr})
+
+        def one(k, cyc):                                   # noqa: F811
+            graph.launch({"x": xs[k % n_data].numpy(), "onehot": ohs[k % n_data].numpy(), "lr": lr})
+            return graph.results()
+        losses.append(float(one(3, None)["loss"][0]))
+        if world > 1:
+            dist.barrier()
+        be.sync()
     launches0 = be.launches()
     t0 = time.perf_counter()
     for k in range(steps):
@@ -188,6 +199,8 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     be.sync(); torch.cuda.synchronize()
     ms = (time.perf_counter() - t0) * 1e3 / steps
     launches = (be.launches() - launches0) // steps
+    if graph:
+        graph.destroy()
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -195,7 +208,8 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     be.reset(0)
     return {"samples_per_s": global_batch / (ms * 1e-3), "ms_per_step": ms, "global_batch": global_batch, "per_rank_batch": B,
             "dispatches_per_step": rp.n_dispatches(rp.cycles[1]), "kernel_launches_per_step": int(launches),
-            "h2d_bytes_per_step": int(B * E * 4 + B * classes * 4 + 4), "loss_first": losses[0], "loss_last": losses[-1],
+            "h2d_bytes_per_step": int(B * E * 4 + B * classes * 4 + 4), "mode": "cuda graph launch per step" if use_graph else "eager replay",
+            "loss_first": losses[0], "loss_last": losses[-1],
             "error": be.last_error()}
 
 
@@ -289,6 +303,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="lenet / vgg workloads: replay call by call instead of one CUDA graph launch per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "lenet", "vgg"],
                     help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet / vgg = only the config-4 / config-5 training steps")
@@ -324,7 +339,7 @@ def main():
         be.shutdown()
         return
     if args.workload in CNN:
-        r = cnn_section(be, stream, rank, world, args.workload, steps=max(args.steps, 1))
+        r = cnn_section(be, stream, rank, world, args.workload, steps=max(args.steps, 1), use_graph=not args.eager)
         if rank == 0:
             what = {"lenet": "cfg4 LeNet-5 SGD step, global batch 1024", "vgg": "cfg5 VGG-style CNN SGD step, 64x64 inputs, global batch 512"}
             print(json.dumps({"metric": f"{args.workload}_train_samples_per_s", "unit": "samples/s", "value": r["samples_per_s"], "n_gpus": world,

@@ -235,6 +235,32 @@ int      thvm_cuda_dp_rank(void);
 int      thvm_cuda_dp_allreduce_sum(const uint32_t *buf_ids, const uint64_t *counts, uint32_t n_bufs);
 void     thvm_cuda_dp_shutdown(void);
 
+/* ---- step capture: record one training step as a CUDA graph, launch it for every later step ----
+ * The counterpart of jit_begin_capture / jit_end_capture / jit_replay (src/tinyhvm.h:1294-1300,
+ * src/backend/metal/jit.m:24-631).  Between capture_begin and capture_end the vtable calls do their
+ * host-side work as usual, but kernels, fills, stream-ordered allocations / frees, copies and NCCL
+ * sums are recorded instead of run.  Rules for the captured step:
+ *   - it has run eagerly at least once (plans built, library scratch grown);
+ *   - it frees every buffer it allocates (a step that ends with pool_reset does) and frees none
+ *     that existed before;
+ *   - data that differs between steps enters through capture_input (returns the input's index,
+ *     -1 on error); host writes made with buf_write are baked into the graph as constants, except
+ *     writes above 1 MiB, which count as inputs in call order; the host memory of an input must be
+ *     valid at every launch (pinned memory keeps the copy asynchronous);
+ *   - buf_read of device data returns zeros while capturing and becomes result k (k counts from 0
+ *     in call order), fetched after a launch with graph_result, which waits for the stream.
+ * capture_end returns a graph handle >= 1, or 0 with the reason in thvm_cuda_last_error(); nothing of
+ * the captured step has run at that point.  graph_launch enqueues the whole step on the backend's
+ * stream.  All other functions return 0 on success. */
+int      thvm_cuda_capture_begin(void);
+int      thvm_cuda_capture_input(uint32_t id, const void *host, uint64_t bytes);
+int      thvm_cuda_capture_end(void);
+int      thvm_cuda_graph_set_input(int graph, int input, const void *host);
+int      thvm_cuda_graph_launch(int graph);
+int      thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes);
+int      thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels);
+void     thvm_cuda_graph_destroy(int graph);
+
 /* ---- index-producing kernels (integer outputs, bit-exact) ----
  * 2x2 stride-2 max-pool of `planes` contiguous [H, W] f32 planes: values to `out_val`
  * ([planes, H/2, W/2] f32) and, when `out_idx` != 0, the position of the winner inside

@@ -212,6 +212,11 @@ def contraction_cases():
         cases.mm_case(rng, 64, 1024, 96), cases.mm_case(rng, 33, 4000, 40),            # few tiles, long K: split-K
         cases.conv_fprop_case(rng, 8, 16, 18, 18, 64, 3), cases.conv_fprop_case(rng, 4, 6, 14, 14, 32, 5),
         cases.conv_wgrad_case(rng, 8, 16, 18, 18, 32, 3),
+        # CTA-pair kernel: >= 256 rows; 256-, 128- and 64-column tiles with ragged edges; long K (split); a wide, short
+        # product computed as its transpose; convolutions with many output positions
+        cases.mm_case(rng, 300, 96, 300), cases.mm_case(rng, 600, 64, 100, ta=True), cases.mm_case(rng, 512, 70, 40, tb=True),
+        cases.mm_case(rng, 256, 2100, 256), cases.mm_case(rng, 40, 130, 700), cases.mm_case(rng, 1024, 256, 512),
+        cases.conv_fprop_case(rng, 8, 16, 18, 18, 64, 3), cases.conv_wgrad_case(rng, 4, 32, 12, 12, 16, 3),
     ]
 
 
@@ -227,3 +232,4 @@ def test_contraction_kernel(cuda, oracle):
     print("plans:", plans)
     assert all(p.startswith("gemm") for p in plans), plans
     assert any("splitk" in p for p in plans), plans
+    assert sum(p.startswith("gemm_pair") for p in plans) >= 6, plans

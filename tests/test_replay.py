@@ -195,3 +195,47 @@ def test_vgg_replay_on_gpu_matches_recorded_run(tmp_path, cuda):
         assert np.allclose(params[n], res[n], rtol=2e-3, atol=2e-5), n
     cuda.reset(0)
     assert cuda.last_error() == ""
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_captured_step_graph_matches_recorded_run(tmp_path, cuda):
+    """Steps 0 and 1 run eagerly; the steady-state cycle is then recorded as a CUDA graph and launched for
+    steps 2..5 with fresh inputs each time: losses and final parameters as in the recorded CPU run."""
+    B, steps = 8, 6
+    path, res, (x, lab, ps) = record(tmp_path, B, steps)
+    recs = replay.load_trace(path)
+    cuda.reset(0)
+    rp = replay.Replayer(replay.CudaTarget(cuda), recs)
+    rp.run_prefix(dict(zip(LENET_NAMES, ps)))
+    lr = np.array([0.01], dtype=np.float32)
+    ext = lambda s: {"x": x[s * B * 784:(s + 1) * B * 784].copy(), "onehot": onehot(lab[s * B:(s + 1) * B], 10), "lr": lr}
+    losses = [float(rp.run(rp.cycles[min(s, 1)], ext(s))["loss"][0]) for s in range(2)]
+    launches_eager = cuda.launches()
+    step = rp.capture(rp.cycles[1], ext(2))
+    assert cuda.launches() - launches_eager == step.n_kernels > 0
+    for s in range(2, steps):
+        step.launch(ext(s))
+        losses.append(float(step.results()["loss"][0]))
+    for s in range(steps):
+        assert abs(losses[s] - float(res[f"loss{s}"][0])) < 2e-5, s
+    for k, (name, shape) in enumerate(zip(LENET_NAMES, LENET_SHAPES)):
+        got = cuda.read(k + 1, np.float32, int(np.prod(shape)))
+        assert np.allclose(got, res[name], rtol=1e-4, atol=1e-6), name
+    step.destroy()
+    cuda.reset(0)
+    assert cuda.last_error() == ""
+
+
+@pytest.mark.gpu
+def test_capture_refuses_a_step_that_leaks_a_buffer(cuda):
+    cuda.reset(0)
+    assert cuda.lib.thvm_cuda_capture_begin() == 0
+    leaked = cuda.alloc(4096)                       # allocated inside the capture and never freed
+    assert cuda.lib.thvm_cuda_capture_end() == 0
+    assert "still live" in cuda.last_error()
+    cuda.lib.thvm_cuda_clear_error()
+    cuda.reset(0)
+    a = cuda.upload(np.arange(1024, dtype=np.float32))
+    assert np.array_equal(cuda.read(a, np.float32, 1024), np.arange(1024, dtype=np.float32))    # the backend is still usable
+    cuda.reset(0)

@@ -1,0 +1,223 @@
+// capture.cu — a whole training step recorded once as a CUDA graph and launched again
+// for every later step: the counterpart of the reference's capture / replay of a step's
+// GPU command sequence (jit_begin_capture / jit_end_capture / jit_replay,
+// src/tinyhvm.h:1294-1300, src/backend/metal/jit.m:24-631), which exists to take the
+// host's per-dispatch work out of the training loop.
+//
+// Between capture_begin and capture_end every vtable call does its host-side work as
+// usual (plan lookup, buffer ids, reference counts) but its stream work — kernels,
+// zero-fills, stream-ordered allocations and frees, copies, NCCL sums — is recorded
+// instead of run.  What differs from an eager step:
+//   * staged host->device writes take their pinned staging space from an arena the graph
+//     owns, so the bytes are still there at every launch (constants of the step);
+//   * data that changes from step to step is declared with capture_input: a copy node
+//     whose host source can be re-pointed before each launch (graph_set_input);
+//   * buf_read of device data records a copy into arena memory and hands back zeros;
+//     the values of a launch are fetched afterwards with graph_result;
+//   * nothing may wait for the stream, so the step must have run eagerly once before
+//     (plans built, scratch grown), and must free every buffer it allocates (a step
+//     that ends with pool_reset does): a graph that still owns memory cannot be
+//     launched twice.
+#include <string.h>
+#include <vector>
+#include "state.h"
+
+namespace thc {
+
+struct Capture {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<uint8_t *> chunks;                 // pinned arena, CHUNK bytes each (large requests get their own)
+    uint64_t chunk_pos = 0, chunk_cap = 0;
+    struct Input { cudaGraphNode_t node; void *dst; uint64_t bytes; const void *src; uint8_t *stage; };
+    struct Result { uint8_t *host; uint64_t bytes; };
+    std::vector<Input> inputs;
+    std::vector<Result> results;
+    uint64_t launches = 0, launches_at_begin = 0;
+    uint32_t first_id = 0;
+    bool failed = false;
+    std::string why;
+};
+
+static std::vector<Capture *> graphs;              // handle = index + 1
+constexpr uint64_t ARENA_CHUNK = 4ull << 20;
+
+bool capturing() { return g.cap != nullptr; }
+
+void capture_fail(const char *why) {
+    if (!g.cap || g.cap->failed) return;
+    g.cap->failed = true;
+    g.cap->why = why;
+}
+
+uint32_t capture_first_id() { return g.cap ? g.cap->first_id : 0; }
+
+uint8_t *capture_arena_take(uint64_t bytes) {
+    Capture &c = *g.cap;
+    bytes = (bytes + 63) & ~63ull;
+    if (c.chunks.empty() || c.chunk_pos + bytes > c.chunk_cap) {
+        const uint64_t cap = bytes > ARENA_CHUNK ? bytes : ARENA_CHUNK;
+        uint8_t *p = nullptr;
+        THC_CUDA_OK(cudaHostAlloc((void **)&p, cap, cudaHostAllocDefault));
+        c.chunks.push_back(p);
+        c.chunk_pos = 0; c.chunk_cap = cap;
+    }
+    uint8_t *p = c.chunks.back() + c.chunk_pos;
+    c.chunk_pos += bytes;
+    return p;
+}
+
+// the node the stream's capture ended on (the operation just issued), or null
+static cudaGraphNode_t last_captured_node() {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    const cudaGraphNode_t *deps = nullptr;
+    size_t n = 0;
+    if (cudaStreamGetCaptureInfo(g.stream, &st, nullptr, nullptr, &deps, &n) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return (st == cudaStreamCaptureStatusActive && n == 1) ? deps[0] : nullptr;
+}
+
+// host -> device copy recorded as an input of the step
+int capture_add_input(void *dst, const void *src, uint64_t bytes) {
+    Capture &c = *g.cap;
+    Capture::Input in{nullptr, dst, bytes, src, nullptr};
+    THC_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream));
+    in.node = last_captured_node();
+    if (!in.node) capture_fail("capture_input: the copy node could not be identified");
+    c.inputs.push_back(in);
+    return (int)c.inputs.size() - 1;
+}
+
+// device -> host read recorded as a result of the step
+void capture_add_result(const void *src, uint64_t bytes) {
+    Capture &c = *g.cap;
+    uint8_t *host = capture_arena_take(bytes);
+    THC_CUDA_OK(cudaMemcpyAsync(host, src, bytes, cudaMemcpyDeviceToHost, g.stream));
+    c.results.push_back({host, bytes});
+}
+
+static void destroy(Capture *c) {
+    if (!c) return;
+    if (c->exec) cudaGraphExecDestroy(c->exec);
+    if (c->graph) cudaGraphDestroy(c->graph);
+    for (uint8_t *p : c->chunks) cudaFreeHost(p);
+    delete c;
+}
+
+void capture_shutdown() {
+    if (g.cap) {
+        cudaGraph_t gr = nullptr;
+        cudaStreamEndCapture(g.stream, &gr);
+        if (gr) cudaGraphDestroy(gr);
+        cudaGetLastError();
+        destroy(g.cap); g.cap = nullptr;
+    }
+    for (Capture *c : graphs) destroy(c);
+    graphs.clear();
+}
+
+static Capture *graph_of(int handle, const char *who) {
+    if (handle < 1 || (size_t)handle > graphs.size() || !graphs[handle - 1]) { set_error("%s: no graph %d", who, handle); return nullptr; }
+    return graphs[handle - 1];
+}
+
+}  // namespace thc
+
+using namespace thc;
+
+extern "C" {
+
+int thvm_cuda_capture_begin(void) {
+    if (!g.ready) { set_error("capture_begin: backend not initialised"); return 1; }
+    if (g.cap) { set_error("capture_begin: a capture is already running"); return 1; }
+    THC_CUDA_OK(cudaStreamSynchronize(g.stream));
+    Capture *c = new Capture();
+    c->first_id = g.count;
+    c->launches_at_begin = g.launches;
+    cudaError_t e = cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed);
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_begin: %s", cudaGetErrorString(e)); delete c; return 1; }
+    g.cap = c;
+    return 0;
+}
+
+int thvm_cuda_capture_input(uint32_t id, const void *host, uint64_t bytes) {
+    if (!g.cap) { set_error("capture_input: no capture is running"); return -1; }
+    Buf &b = buf_for_output(id, "capture_input", bytes);
+    if (bytes > b.bytes || bytes == 0) { set_error("capture_input: %llu bytes into buffer %u of %llu", (unsigned long long)bytes, id, (unsigned long long)b.bytes); return -1; }
+    mark_device_written(id);                       // the host shadow no longer speaks for this buffer
+    return capture_add_input(b.ptr, host, bytes);
+}
+
+int thvm_cuda_capture_end(void) {
+    if (!g.cap) { set_error("capture_end: no capture is running"); return 0; }
+    Capture *c = g.cap;
+    for (uint32_t i = c->first_id; i < THC_MAX_BUFS && !c->failed; i++)
+        if (g.bufs[i].live && g.bufs[i].ptr && !g.bufs[i].plain_alloc)
+            capture_fail("a buffer allocated inside the captured step is still live: the step must free what it allocates (end with pool_reset)");
+    c->launches = g.launches - c->launches_at_begin;
+    cudaError_t e = cudaStreamEndCapture(g.stream, &c->graph);
+    g.cap = nullptr;
+    // buffers the step left behind point into memory of a graph that will never run: forget them
+    // (no free call: the addresses belong to the graph) and rewind the ids, as if the step had not happened
+    auto forget_leftovers = [&]() {
+        for (uint32_t i = c->first_id; i < THC_MAX_BUFS; i++)
+            if (g.bufs[i].live) { free(g.bufs[i].shadow); g.bufs[i] = Buf(); }
+        if (g.count > c->first_id) g.count = c->first_id;
+    };
+    if (e != cudaSuccess || !c->graph) { cudaGetLastError(); set_error("capture_end: %s", cudaGetErrorString(e)); forget_leftovers(); destroy(c); return 0; }
+    if (c->failed) { set_error("capture_end: %s", c->why.c_str()); forget_leftovers(); destroy(c); return 0; }
+    e = cudaGraphInstantiate(&c->exec, c->graph, 0);
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_end: cudaGraphInstantiate: %s", cudaGetErrorString(e)); destroy(c); return 0; }
+    graphs.push_back(c);
+    return (int)graphs.size();
+}
+
+int thvm_cuda_graph_set_input(int graph, int input, const void *host) {
+    Capture *c = graph_of(graph, "graph_set_input");
+    if (!c) return 1;
+    if (input < 0 || (size_t)input >= c->inputs.size() || !host) { set_error("graph_set_input: input %d of %zu", input, c->inputs.size()); return 1; }
+    Capture::Input &in = c->inputs[input];
+    if (in.src == host) return 0;
+    cudaError_t e = cudaGraphExecMemcpyNodeSetParams1D(c->exec, in.node, in.dst, host, in.bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("graph_set_input: %s", cudaGetErrorString(e)); return 1; }
+    in.src = host;
+    return 0;
+}
+
+int thvm_cuda_graph_launch(int graph) {
+    Capture *c = graph_of(graph, "graph_launch");
+    if (!c) return 1;
+    if (g.cap) { set_error("graph_launch: a capture is running"); return 1; }
+    cudaError_t e = cudaGraphLaunch(c->exec, g.stream);
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("graph_launch: %s", cudaGetErrorString(e)); return 1; }
+    g.launches += c->launches;
+    return 0;
+}
+
+int thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes) {
+    Capture *c = graph_of(graph, "graph_result");
+    if (!c) return 1;
+    if (result < 0 || (size_t)result >= c->results.size()) { set_error("graph_result: result %d of %zu", result, c->results.size()); return 1; }
+    THC_CUDA_OK(cudaStreamSynchronize(g.stream));
+    const Capture::Result &r = c->results[result];
+    memcpy(out, r.host, bytes < r.bytes ? bytes : r.bytes);
+    if (bytes > r.bytes) memset((uint8_t *)out + r.bytes, 0, bytes - r.bytes);
+    return 0;
+}
+
+int thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels) {
+    Capture *c = graph_of(graph, "graph_counts");
+    if (!c) return 1;
+    if (n_inputs) *n_inputs = (uint32_t)c->inputs.size();
+    if (n_results) *n_results = (uint32_t)c->results.size();
+    if (n_kernels) *n_kernels = c->launches;
+    return 0;
+}
+
+void thvm_cuda_graph_destroy(int graph) {
+    if (graph < 1 || (size_t)graph > graphs.size() || !graphs[graph - 1]) return;
+    if (g.ready) cudaStreamSynchronize(g.stream);
+    destroy(graphs[graph - 1]);
+    graphs[graph - 1] = nullptr;
+}
+
+}  // extern "C"

@@ -34,6 +34,7 @@ struct GemmDesc {
     uint32_t debug_mode;               // timing experiments only: 1 = MMAs without operand traffic, 2 = operand traffic without MMAs
     uint32_t band, prefetch;           // tile-order band height (row tiles); L2 prefetch on/off
     uint32_t kb_chunk;                 // k-blocks (of 32) per split; gridDim.z splits share one output tile
+    uint32_t n_half;                   // CTA-pair kernel: B rows (output columns) each CTA of a pair loads: 128, 64 or 32
     float *partial;                    // split-K: dense [split][M][N] partial sums (library scratch), else null
     const float *A, *B;                // filled per launch
     float *C;

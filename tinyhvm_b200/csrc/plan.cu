@@ -150,7 +150,8 @@ static bool build_desc(Plan *p, const thc_view_t **views, const thc_tracker_t *c
         uint64_t bytes = trackers.size() * sizeof(DTracker);
         THC_CUDA_OK(cudaMallocAsync((void **)&p->dev_trackers, bytes, g.stream));
         THC_CUDA_OK(cudaMemcpyAsync(p->dev_trackers, trackers.data(), bytes, cudaMemcpyHostToDevice, g.stream));
-        THC_CUDA_OK(cudaStreamSynchronize(g.stream));   // `trackers` dies with this scope
+        if (capturing()) capture_fail("a plan was built inside the captured step: run the step once before capturing it");
+        else THC_CUDA_OK(cudaStreamSynchronize(g.stream));   // `trackers` dies with this scope
         D.trackers = p->dev_trackers;
     }
     return true;

@@ -60,7 +60,12 @@ Buf &buf_checked(uint32_t id, const char *who) {
     if (!b.ptr) {                                   // host-only so far: attach device memory now
         uint64_t sz = (b.bytes + 15) & ~15ull;
         if (sz == 0) sz = 16;
-        THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
+        if (g.cap && id < capture_first_id()) {     // outlives the captured step: must not become memory the graph owns
+            THC_CUDA_OK(cudaMalloc(&b.ptr, sz));
+            b.plain_alloc = true;
+        } else {
+            THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
+        }
         if (b.shadow && b.shadow_valid && b.bytes) {
             uint8_t *stage = ring_take(sz);
             memset(stage, 0, sz);
@@ -85,6 +90,7 @@ Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written) {
 
 void *scratch_reserve(uint64_t bytes) {
     if (bytes <= g.scratch_bytes) return g.scratch;
+    if (g.cap) { capture_fail("library scratch had to grow inside the captured step: run the step once before capturing it"); return g.scratch; }
     if (g.scratch) THC_CUDA_OK(cudaFreeAsync(g.scratch, g.stream));
     uint64_t want = bytes + (bytes >> 2);
     THC_CUDA_OK(cudaMallocAsync(&g.scratch, want, g.stream));
@@ -103,7 +109,7 @@ void after_launch(const char *plan) {
     if (e != cudaSuccess) fatal("launch of %s failed: %s", plan, cudaGetErrorString(e));
     g.launches++;
     g.last_plan = plan;
-    if (g.profile) {
+    if (g.profile && !g.cap) {
         if (!plan_stats) plan_stats = new std::map<std::string, PlanStat>();
         PlanStat &s = (*plan_stats)[plan];
         s.launches++;
@@ -117,13 +123,14 @@ void after_launch(const char *plan) {
     }
 }
 void profile_begin() {             // called by dispatchers right before a launch when profiling
-    if (!g.profile) return;
+    if (!g.profile || g.cap) return;
     if (!prof_ev[0]) { cudaEventCreate(&prof_ev[0]); cudaEventCreate(&prof_ev[1]); }
     THC_CUDA_OK(cudaEventRecord(prof_ev[0], g.stream));
     prof_open = true;
 }
 
 static void check_device_status(const char *who) {
+    if (g.cap) return;                                 // nothing may wait for the stream while it records
     int st = 0;
     THC_CUDA_OK(cudaMemcpyAsync(&st, g.dev_status, sizeof st, cudaMemcpyDeviceToHost, g.stream));
     THC_CUDA_OK(cudaStreamSynchronize(g.stream));
@@ -135,6 +142,7 @@ static void check_device_status(const char *who) {
 
 // ---- staging ring ----
 static uint8_t *ring_take(uint64_t bytes) {
+    if (g.cap) return capture_arena_take(bytes);       // a captured copy reads its staging bytes again at every launch
     const uint64_t half = g.ring_bytes / 2;
     bytes = (bytes + 63) & ~63ull;
     unsigned cur = (unsigned)(g.ring_pos / half);
@@ -212,7 +220,12 @@ int thvm_cuda_init(void) {
 
 static void release(uint32_t id) {
     Buf &b = g.bufs[id];
-    if (b.ptr) THC_CUDA_OK(cudaFreeAsync(b.ptr, g.stream));
+    if (b.ptr && g.cap && id < capture_first_id())
+        capture_fail("the captured step frees a buffer that was allocated before the capture began");
+    if (b.ptr) {
+        if (b.plain_alloc) THC_CUDA_OK(cudaFree(b.ptr));
+        else THC_CUDA_OK(cudaFreeAsync(b.ptr, g.stream));
+    }
     free(b.shadow);
     b = Buf();
 }
@@ -222,6 +235,7 @@ void thvm_cuda_dp_shutdown(void);   // dp.cu
 
 void thvm_cuda_shutdown(void) {
     if (!g.ready) return;
+    capture_shutdown();
     thvm_cuda_dp_shutdown();
     cudaStreamSynchronize(g.stream);
     for (uint32_t i = 1; i < g.count; i++) if (g.bufs[i].live) release(i);
@@ -305,6 +319,7 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
         // Large payloads go straight from the caller's memory (full PCIe rate
         // when it is pinned) and the call waits for the DMA, after which the
         // caller may reuse the source.
+        if (g.cap) { capture_add_input(b.ptr, data, bytes); return; }   // an input of the captured step: the caller keeps `data` alive
         THC_CUDA_OK(cudaMemcpyAsync(b.ptr, data, bytes, cudaMemcpyHostToDevice, g.stream));
         THC_CUDA_OK(cudaStreamSynchronize(g.stream));
     }
@@ -317,6 +332,7 @@ static void read_impl(uint32_t id, void *out, uint64_t bytes, bool sync) {
     if (n == 0) return;
     if (b.shadow && b.shadow_valid) { memcpy(out, b.shadow, n); return; }
     if (!b.ptr || b.zero_pending) { memset(out, 0, n); return; }
+    if (g.cap) { capture_add_result(b.ptr, n); memset(out, 0, n); return; }   // values come from graph_result after a launch
     THC_CUDA_OK(cudaMemcpyAsync(out, b.ptr, n, cudaMemcpyDeviceToHost, g.stream));
     if (sync) check_device_status("buf_read");                // drains the stream
 }
@@ -374,7 +390,7 @@ const char *thvm_cuda_last_error(void) {
 }
 void thvm_cuda_clear_error(void) { g.last_error.clear(); }
 void *thvm_cuda_stream(void) { return (void *)g.stream; }
-void thvm_cuda_sync(void) { if (g.ready) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
+void thvm_cuda_sync(void) { if (g.ready && !g.cap) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
 void *thvm_cuda_buf_ptr(uint32_t id) {
     if (!(g.ready && id && id < THC_MAX_BUFS && g.bufs[id].live)) return nullptr;
     Buf &b = buf_checked(id, "buf_ptr");    // attaches device memory if the buffer was host-only

@@ -21,7 +21,10 @@ struct Buf {
     uint8_t *shadow   = nullptr;   // host copy of a small host-written buffer
     bool     shadow_valid = false; // false once a kernel or copy wrote the buffer
     bool     zero_pending = false; // fresh device memory whose zero-fill has not been issued yet
+    bool     plain_alloc = false;  // ptr came from cudaMalloc (attached while a step was being captured), not from the stream-ordered pool
 };
+
+struct Capture;                    // capture.cu: the step being recorded as a CUDA graph
 
 struct State {
     bool         ready = false;
@@ -31,6 +34,7 @@ struct State {
     Buf          bufs[THC_MAX_BUFS];
     uint32_t     count = 1;          // next id; 0 is the null buffer
     uint32_t     persistent = 0;     // ids <= this survive decref
+    Capture     *cap = nullptr;      // non-null while a step is being captured
     // pinned staging ring for small host->device writes
     uint8_t     *ring = nullptr;
     uint64_t     ring_bytes = 0, ring_pos = 0;
@@ -91,5 +95,15 @@ void profile_begin();
 void after_launch(const char *plan);
 // host -> device copy of a small block through the pinned staging ring
 void upload_small(void *dev_dst, const void *src, uint64_t bytes);
+
+// ---- step capture (capture.cu) ----
+bool capturing();
+// mark the running capture unusable (capture_end will then fail with this reason); no-op outside a capture
+void capture_fail(const char *why);
+uint32_t capture_first_id();                                    // first buffer id handed out inside the capture
+uint8_t *capture_arena_take(uint64_t bytes);                    // pinned host memory that lives as long as the graph
+int  capture_add_input(void *dst, const void *src, uint64_t bytes);
+void capture_add_result(const void *src, uint64_t bytes);
+void capture_shutdown();
 
 }  // namespace thc

@@ -11,6 +11,9 @@ src/tinyhvm.h:1294-1300), and the way the CNN training configs are benchmarked
 here.  Traces are recorded by oracle/ref_trace.c (test infrastructure, needs the
 reference checkout) and committed under tinyhvm_b200/traces/.
 
+`Replayer.capture` records a cycle once as a CUDA graph (CapturedStep); every later
+step is then a single graph launch.
+
 Layout of a trace: 8-byte header, then records `u32 op, u32 bytes, payload`.
 Host writes larger than 8 KiB, and the ones the driver named (inputs, one-hot
 labels, parameters, the learning rate), carry no data: the caller supplies them
@@ -137,6 +140,73 @@ class CudaTarget:
         assert rc == 0, self.be.last_error()
 
 
+class CapturedStep:
+    """One steady-state cycle of a trace recorded as a CUDA graph (thvm_cuda_capture_*): `launch(externals)`
+    points the graph's inputs at this step's host arrays (keep them alive, ideally pinned, until the results
+    have been fetched) and enqueues the whole step with one call; `results()` waits and returns the named
+    reads.  The cycle must have been replayed eagerly before (plans built, scratch grown)."""
+
+    def __init__(self, rp: "Replayer", recs, externals: dict):
+        t = rp.t
+        assert isinstance(t, CudaTarget), "step capture needs the CUDA library"
+        self.lib, self.be = t.lib, t.be
+        self.inputs, self.reads, used = [], [], {}
+        assert self.lib.thvm_cuda_capture_begin() == 0, self.be.last_error()
+        for item in rp._bind(recs):
+            kind = item[0]
+            if kind == "call":
+                item[1](*item[2])
+            elif kind == "alloc":
+                got = t.alloc(item[2])
+                assert got == item[1], f"buffer id {got} where the trace has {item[1]}: pool out of step with the recording"
+            elif kind == "ext":
+                _, i, nb, name = item
+                k = used.get(name, 0); used[name] = k + 1
+                src = externals[name]
+                src = src[k % len(src)] if isinstance(src, (list, tuple)) else src
+                assert src.nbytes == nb, f"external {name}: {src.nbytes} bytes supplied, trace wants {nb}"
+                idx = self.lib.thvm_cuda_capture_input(i, src.ctypes.data, nb)
+                assert idx == len(self.inputs), self.be.last_error()
+                self.inputs.append((name, k, nb))
+            elif kind == "read":
+                _, i, nb, name = item
+                scratch = np.empty(nb, dtype=np.uint8)
+                t.read(i, scratch.ctypes.data, nb)          # recorded as a result of the graph (or served from a host shadow)
+                self.reads.append((name, nb))
+        self.handle = self.lib.thvm_cuda_capture_end()
+        assert self.handle > 0, self.be.last_error()
+        ni, nr, nk = C.c_uint32(), C.c_uint32(), C.c_uint64()
+        self.lib.thvm_cuda_graph_counts(self.handle, C.byref(ni), C.byref(nr), C.byref(nk))
+        assert ni.value == len(self.inputs)
+        self.n_results, self.n_kernels = nr.value, nk.value
+        # reads that were served from a host shadow never became graph results; the trace's training steps have none
+        assert self.n_results == len(self.reads), "a read inside the captured step did not come from the device"
+
+    def launch(self, externals: dict):
+        self._alive = []
+        for idx, (name, k, nb) in enumerate(self.inputs):
+            src = externals[name]
+            src = src[k % len(src)] if isinstance(src, (list, tuple)) else src
+            assert src.nbytes == nb
+            self._alive.append(src)
+            assert self.lib.thvm_cuda_graph_set_input(self.handle, idx, src.ctypes.data) == 0, self.be.last_error()
+        assert self.lib.thvm_cuda_graph_launch(self.handle) == 0, self.be.last_error()
+
+    def results(self) -> dict:
+        out = {}
+        for k, (name, nb) in enumerate(self.reads):
+            buf = np.empty(nb, dtype=np.uint8)
+            assert self.lib.thvm_cuda_graph_result(self.handle, k, buf.ctypes.data, nb) == 0, self.be.last_error()
+            if name:
+                out[name] = buf.view(np.float32) if nb % 4 == 0 else buf
+        return out
+
+    def destroy(self):
+        if self.handle:
+            self.lib.thvm_cuda_graph_destroy(self.handle)
+            self.handle = 0
+
+
 class Replayer:
     """Binds a trace to a target once; `run(cycle, externals)` then replays one cycle.
 
@@ -210,6 +280,9 @@ class Replayer:
                 if name:
                     reads[name] = out.view(np.float32) if nb % 4 == 0 else out
         return reads
+
+    def capture(self, recs, externals: dict) -> CapturedStep:
+        return CapturedStep(self, recs, externals)
 
     def run_prefix(self, externals: dict) -> dict:
         return self.run(self.prefix, externals)
