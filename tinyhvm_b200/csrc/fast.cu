@@ -43,6 +43,16 @@ constexpr ChainDef CHAINS[] = {
     {1, 0, {}, {}, {}},                                                            // 6: copy / plain reduce
     {2, 1, {THC_SUB}, {0}, {1}},                                                   // 7: a-b
     {2, 2, {THC_SUB, THC_EXP}, {0, 2}, {1, 2}},                                    // 8: exp(a-b)
+    // the batch-norm / pooling / SGD chains of the CNN training steps
+    {4, 3, {THC_SUB, THC_SUB, THC_MUL}, {0, 2, 4}, {1, 3, 5}},                     // 9: (a-b)*(c-d)      variance terms
+    {3, 2, {THC_SUB, THC_MUL}, {0, 3}, {1, 2}},                                    // 10: (a-b)*c         normalise
+    {3, 2, {THC_MUL, THC_ADD}, {0, 3}, {1, 2}},                                    // 11: a*b+c           scale and shift
+    {1, 1, {THC_RELU}, {0}, {0}},                                                  // 12: relu(a)
+    {3, 2, {THC_CMP, THC_MUL}, {1, 0}, {2, 3}},                                    // 13: a*(b>c)         relu backward
+    {8, 7, {THC_MUL, THC_MUL, THC_MUL, THC_SUB, THC_MUL, THC_SUB, THC_MUL}, {0, 8, 3, 10, 6, 11, 9}, {1, 2, 4, 5, 7, 12, 13}},
+                                                                                   // 14: a*b*c * ((d*e - f) - g*h)   batch-norm backward
+    {4, 3, {THC_CMP, THC_SUB, THC_MUL}, {2, 1, 0}, {3, 4, 5}},                     // 15: a*(b-(c>d))     max-pool backward (ties all pass)
+    {3, 2, {THC_MUL, THC_SUB}, {1, 0}, {2, 3}},                                    // 16: a-b*c           SGD update
 };
 constexpr int N_CHAINS = sizeof(CHAINS) / sizeof(CHAINS[0]);
 
@@ -596,6 +606,7 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
 
 void classify_plan(Plan *p) {
     if (try_contraction(p)) return;
+    if (try_pool2x2(p)) return;
     FastDesc *F = new FastDesc();
     if (build_fast(p->host, *F)) { p->fast = (struct FastDesc *)F; p->kind = F->strategy == 0 ? PLAN_EW : PLAN_REDUCE; }
     else { delete F; p->fast = nullptr; p->kind = PLAN_GENERIC; }
@@ -647,6 +658,7 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
 
 bool launch_fast(Plan *p, const GenArgs &args) {
     if (p->kind == PLAN_CONTRACT) return launch_contraction(p, args);
+    if (p->kind == PLAN_POOL) return launch_pool2x2(p, args);
     FastDesc &F = *(FastDesc *)p->fast;
     FDesc D = F.d;
     for (unsigned i = 0; i < D.prog.n_leaves; i++) {
@@ -679,6 +691,14 @@ bool launch_fast(Plan *p, const GenArgs &args) {
         case 6: launch_with<StaticEval<6>>(F, D, out); break;
         case 7: launch_with<StaticEval<7>>(F, D, out); break;
         case 8: launch_with<StaticEval<8>>(F, D, out); break;
+        case 9: launch_with<StaticEval<9>>(F, D, out); break;
+        case 10: launch_with<StaticEval<10>>(F, D, out); break;
+        case 11: launch_with<StaticEval<11>>(F, D, out); break;
+        case 12: launch_with<StaticEval<12>>(F, D, out); break;
+        case 13: launch_with<StaticEval<13>>(F, D, out); break;
+        case 14: launch_with<StaticEval<14>>(F, D, out); break;
+        case 15: launch_with<StaticEval<15>>(F, D, out); break;
+        case 16: launch_with<StaticEval<16>>(F, D, out); break;
         default: launch_with<InterpEval>(F, D, out); break;
     }
     after_launch(F.flat ? F.flat_name : F.name);

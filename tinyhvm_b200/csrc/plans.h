@@ -10,6 +10,7 @@ enum PlanKind : int {
     PLAN_EW,            // collapsed-dims elementwise, vectorised inner dim (ew.cu)
     PLAN_REDUCE,        // collapsed-dims reduce (reduce.cu)
     PLAN_CONTRACT,      // SUM(MUL(a,b)) with separable operands -> GEMM (gemm.cu)
+    PLAN_POOL,          // RMAX over the 2x2 windows of contiguous planes -> pooling kernel (uop.cu)
 };
 
 struct FastDesc;        // family-specific, defined in fast_desc.h
@@ -22,6 +23,9 @@ struct Plan {
     uint32_t   n_trackers = 0;
     FastDesc  *fast = nullptr;          // owned; null for PLAN_GENERIC
     void      *contract = nullptr;      // owned (gemm.cu); set for PLAN_CONTRACT
+    unsigned long long pool_planes = 0; // PLAN_POOL: contiguous [planes, pool_h, pool_w] input starting at element pool_off
+    uint32_t   pool_h = 0, pool_w = 0;
+    long long  pool_off = 0;
 };
 
 // Decide the family for a freshly built plan (sets kind / fast).
@@ -33,5 +37,8 @@ void free_fast(Plan *p);
 bool try_contraction(Plan *p);
 bool launch_contraction(Plan *p, const GenArgs &args);
 void free_contraction(Plan *p);
+// RMAX over 2x2 stride-2 windows of contiguous planes -> pooling kernel (uop.cu)
+bool try_pool2x2(Plan *p);
+bool launch_pool2x2(Plan *p, const GenArgs &args);
 
 }  // namespace thc

@@ -13,6 +13,7 @@
 // adam_step follows the arithmetic of the reference's Metal kernel
 // (src/shaders.metal:406-420), the only definition of that vtable slot.
 #include "device_common.cuh"
+#include "plans.h"
 #include "state.h"
 
 namespace thc {
@@ -126,8 +127,17 @@ __global__ void __launch_bounds__(256) k_adam(float *__restrict__ p, const float
 // (0,0),(0,1),(1,0),(1,1), strict '>' so the first maximum wins, index stored as u8 0..3
 // (the arithmetic of the reference's max-pool shader, src/shaders.metal:427-458).
 // One thread per pair of neighbouring outputs: two 16-byte loads (one per input row).
+// (value, index) of a window scanned in order w0..w3 with strict '>'.  `floor`: start from the RMAX identity
+// -1e30f instead of from w0, which is what a reduce dispatch computes (src/backend/cpu/dispatch.c:148-151, 202-217).
+__device__ __forceinline__ void pick4(float w0, float w1, float w2, float w3, bool floor, float &best, uint8_t &bi) {
+    best = floor ? -1e30f : w0; bi = 0;
+    if (floor && w0 > best) best = w0;
+    if (w1 > best) { best = w1; bi = 1; }
+    if (w2 > best) { best = w2; bi = 2; }
+    if (w3 > best) { best = w3; bi = 3; }
+}
 __global__ void __launch_bounds__(256) k_maxpool2x2_index(const float *__restrict__ x, float *__restrict__ y, uint8_t *__restrict__ idx,
-                                                          unsigned long long planes, unsigned H, unsigned W, unsigned vec) {
+                                                          unsigned long long planes, unsigned H, unsigned W, unsigned vec, unsigned floor) {
     const unsigned OH = H / 2, OW = W / 2;
     const unsigned per_row = vec ? OW / 2 : OW;                      // work items per output row
     const unsigned long long items = planes * OH * per_row;
@@ -142,22 +152,14 @@ __global__ void __launch_bounds__(256) k_maxpool2x2_index(const float *__restric
         const unsigned long long o = rowi * OW;
         if (vec) {
             const float4 a = *reinterpret_cast<const float4 *>(r0 + 4u * c), b = *reinterpret_cast<const float4 *>(r1 + 4u * c);
-            float b0 = a.x; uint8_t i0 = 0;
-            if (a.y > b0) { b0 = a.y; i0 = 1; }
-            if (b.x > b0) { b0 = b.x; i0 = 2; }
-            if (b.y > b0) { b0 = b.y; i0 = 3; }
-            float b1 = a.z; uint8_t i1 = 0;
-            if (a.w > b1) { b1 = a.w; i1 = 1; }
-            if (b.z > b1) { b1 = b.z; i1 = 2; }
-            if (b.w > b1) { b1 = b.w; i1 = 3; }
+            float b0, b1; uint8_t i0, i1;
+            pick4(a.x, a.y, b.x, b.y, floor != 0, b0, i0);
+            pick4(a.z, a.w, b.z, b.w, floor != 0, b1, i1);
             *reinterpret_cast<float2 *>(y + o + 2u * c) = make_float2(b0, b1);
             if (idx) { idx[o + 2u * c] = i0; idx[o + 2u * c + 1] = i1; }
         } else {
-            const float w0 = r0[2u * c], w1 = r0[2u * c + 1], w2 = r1[2u * c], w3 = r1[2u * c + 1];
-            float best = w0; uint8_t bi = 0;
-            if (w1 > best) { best = w1; bi = 1; }
-            if (w2 > best) { best = w2; bi = 2; }
-            if (w3 > best) { best = w3; bi = 3; }
+            float best; uint8_t bi;
+            pick4(r0[2u * c], r0[2u * c + 1], r1[2u * c], r1[2u * c + 1], floor != 0, best, bi);
             y[o + c] = best;
             if (idx) idx[o + c] = bi;
         }
@@ -187,6 +189,44 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float *__restrict__ x
         }
         if (lane == 0) out[r] = bi;
     }
+}
+
+// ---- the RMAX dispatch of a 2x2 stride-2 pool (thvm_maxpool2d, src/nn/conv.c:484-513) on the pooling kernel ----
+// Recognised shape: one unmasked f32 leaf, no ops, RMAX over the last two dims (2, 2), the leaf a window view of
+// contiguous [planes, H, W] memory: strides (..., 2W, 2, W, 1) over (..., OH, OW, 2, 2) with H = 2 OH, W = 2 OW.
+bool try_pool2x2(Plan *p) {
+    const GenDesc &H = p->host;
+    if (!H.has_reduce || H.reduce_type != THC_RMAX || H.n_leaves != 1 || H.n_ops != 0 || H.post_start || H.out_dtype != THC_F32) return false;
+    const DLeaf &L = H.leaves[0];
+    const int r = (int)H.rank;
+    if (L.dtype != THC_F32 || L.tracker >= 0 || L.v.has_mask || L.v.n_cm || r < 4 || (int)L.v.rank != r) return false;
+    if (H.n_rdims != 2 || (int)H.rdim[0] != r - 2 || (int)H.rdim[1] != r - 1) return false;
+    for (int d = 0; d < r; d++) if (L.v.dims[d] != H.full_dims[d]) return false;
+    if (H.full_dims[r - 1] != 2 || H.full_dims[r - 2] != 2) return false;
+    const unsigned long long OW = H.full_dims[r - 3], OH = H.full_dims[r - 4], W = 2 * OW, Hh = 2 * OH;
+    if (L.v.strides[r - 1] != 1 || L.v.strides[r - 2] != (long long)W || L.v.strides[r - 3] != 2 || L.v.strides[r - 4] != (long long)(2 * W)) return false;
+    unsigned long long planes = 1, want = Hh * W;
+    for (int d = r - 5; d >= 0; d--) {
+        if (H.full_dims[d] != 1 && (unsigned long long)L.v.strides[d] != want) return false;
+        planes *= H.full_dims[d]; want *= H.full_dims[d];
+    }
+    if (L.v.offset < 0 || Hh > 0xFFFFFFFFull || W > 0xFFFFFFFFull) return false;
+    p->pool_planes = planes; p->pool_h = (uint32_t)Hh; p->pool_w = (uint32_t)W; p->pool_off = L.v.offset;
+    p->kind = PLAN_POOL;
+    return true;
+}
+
+bool launch_pool2x2(Plan *p, const GenArgs &args) {
+    const unsigned long long in_n = p->pool_planes * p->pool_h * p->pool_w;
+    if ((unsigned long long)p->pool_off + in_n > args.cap[0]) return false;         // would leave the buffer: the checked generic kernel runs
+    const float *x = (const float *)args.leaf[0] + p->pool_off;
+    const unsigned vec = (p->pool_w % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(args.out) & 7u) == 0) ? 1u : 0u;
+    const uint64_t items = p->pool_planes * (p->pool_h / 2) * (vec ? p->pool_w / 4 : p->pool_w / 2);
+    if (g.profile_level >= 2) snprintf(g.last_shape, sizeof g.last_shape, "planes=%llu H=%u W=%u vec=%u", p->pool_planes, p->pool_h, p->pool_w, vec);
+    profile_begin();
+    k_maxpool2x2_index<<<grid_for(items, 256, 8), 256, 0, g.stream>>>(x, (float *)args.out, nullptr, p->pool_planes, p->pool_h, p->pool_w, vec, 1u);
+    after_launch("pool2x2_rmax");
+    return true;
 }
 
 }  // namespace thc
@@ -265,7 +305,7 @@ int thvm_cuda_maxpool2x2_index(uint32_t out_val, uint32_t out_idx, uint32_t x, u
     const uint64_t items = (uint64_t)planes * (H / 2) * (vec ? W / 4 : W / 2);
     profile_begin();
     k_maxpool2x2_index<<<grid_for(items, 256, 8), 256, 0, g.stream>>>((const float *)bx.ptr, (float *)by.ptr, bi ? (uint8_t *)bi->ptr : nullptr,
-                                                                     planes, H, W, vec);
+                                                                     planes, H, W, vec, 0u);
     after_launch("maxpool2x2_index");
     return 0;
 }
