@@ -200,6 +200,7 @@ __global__ void __launch_bounds__(256) k_ew(const __grid_constant__ FDesc D, flo
         float res[V];
         eval_at<EV, V>(D, c, flat, res);
         if (V == 4) *reinterpret_cast<float4 *>(out + flat) = make_float4(res[0], res[1], res[2], res[3]);
+        else if (V == 2) *reinterpret_cast<float2 *>(out + flat) = make_float2(res[0], res[1]);
         else out[flat] = res[0];
     }
 }
@@ -387,6 +388,91 @@ __global__ void __launch_bounds__(256) k_ew_flat(const __grid_constant__ FDesc D
     }
 }
 
+// ------------------------------------------------------------------ row kernels: contiguous rows with per-row constants
+// The iteration space seen as R rows of dims[in] elements, every leaf either walking the row with stride 1
+// (16-byte loads) or constant along it (a per-channel statistic, a scalar): coordinates are decoded once per
+// row, not per vector, and a row's loads are issued back to back.  Elementwise: the output row is contiguous.
+// Reduce (the innermost dim and any outer dims reduced): each row yields one partial sum, written to slot
+// o * row_split + s (o = index over the kept outer dims, s = index over the reduced outer dims); k_red_final
+// adds the row_split partials of an output in fixed order.  This is the shape of every batch-norm kernel:
+// [B, C, H*W] with [1, C, 1] statistics.
+template <class EV, int G, bool RED>
+__global__ void __launch_bounds__(256) k_rowsx(const __grid_constant__ FDesc D, float *__restrict__ out) {
+    constexpr int U = flat_unroll<EV>();
+    constexpr int NL = EV::MAXL;
+    __shared__ float part[8];
+    const int nl = EV::nleaves(D.prog);
+    const int in = (int)D.rank - 1;
+    const unsigned rtype = D.rtype;
+    const unsigned cols4 = D.dims[in] / 4;
+    const unsigned lane = threadIdx.x % G;
+    const unsigned long long R = D.numel / D.dims[in];
+    const unsigned long long per_cta = 256 / G;
+    float4 *o4 = reinterpret_cast<float4 *>(out);
+    for (unsigned long long row = (unsigned long long)blockIdx.x * per_cta + threadIdx.x / G; row < R;
+         row += (unsigned long long)gridDim.x * per_cta) {
+        unsigned c[FR];
+        {
+            unsigned long long rem = row;
+            for (int d = in - 1; d > 0; d--) { const unsigned long long q = rem / D.dims[d]; c[d] = (unsigned)(rem - q * D.dims[d]); rem = q; }
+            c[0] = (unsigned)rem;
+        }
+        FlatLeaves<EV> LV;
+#pragma unroll
+        for (int i = 0; i < NL; i++) {
+            LV.fl[i] = false; LV.sc[i] = 0.0f; LV.p[i] = nullptr;
+            if (i < nl) {
+                const FLeaf &L = D.leaf[i];
+                long long off = L.off;
+                for (int d = 0; d < in; d++) off += (long long)c[d] * L.stride[d];
+                LV.fl[i] = L.stride[in] == 1;
+                if (LV.fl[i]) LV.p[i] = reinterpret_cast<const float4 *>(L.ptr + off);
+                else LV.sc[i] = L.ptr[off];
+            }
+        }
+        float acc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) acc[u] = red_init(rtype);
+        unsigned i = lane;
+        for (; i + (U - 1) * G < cols4; i += U * G) {
+            float4 r[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) r[u] = LV.eval(D, i + u * G);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (RED) acc[u] = red_combine(rtype, acc[u], red_combine(rtype, red_combine(rtype, r[u].x, r[u].y), red_combine(rtype, r[u].z, r[u].w)));
+                else o4[row * cols4 + i + u * G] = r[u];
+            }
+        }
+        for (; i < cols4; i += G) {
+            const float4 r = LV.eval(D, i);
+            if (RED) acc[0] = red_combine(rtype, acc[0], red_combine(rtype, red_combine(rtype, r.x, r.y), red_combine(rtype, r.z, r.w)));
+            else o4[row * cols4 + i] = r;
+        }
+        if (RED) {
+            float a = acc[0];
+#pragma unroll
+            for (int u = 1; u < U; u++) a = red_combine(rtype, a, acc[u]);
+#pragma unroll
+            for (int w = 16; w > 0; w >>= 1) a = red_combine(rtype, a, __shfl_down_sync(0xffffffffu, a, w));
+            unsigned long long slot = 0;
+            for (int d = 0; d < in; d++) slot += (unsigned long long)c[d] * (D.omul[d] * D.row_split + D.smul[d]);
+            if (G == 256) {                   // one row per CTA: the barriers are uniform
+                __syncthreads();
+                if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = a;
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    a = part[0];
+                    for (int w = 1; w < 8; w++) a = red_combine(rtype, a, part[w]);
+                    out[slot] = a;
+                }
+            } else if (lane == 0) {
+                out[slot] = a;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ reduce, innermost dim kept
 template <class EV>
 __global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc D, float *__restrict__ out) {
@@ -421,6 +507,20 @@ __global__ void __launch_bounds__(256) k_red_outer(const __grid_constant__ FDesc
     }
 }
 
+// second pass with many partials per output: one warp per output, lanes stride over the partials, fixed tree
+__global__ void __launch_bounds__(256) k_red_final_warp(const float *__restrict__ partial, float *__restrict__ out,
+                                                        unsigned long long n_out, unsigned split, unsigned rtype) {
+    const unsigned lane = threadIdx.x & 31;
+    for (unsigned long long o = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; o < n_out;
+         o += ((unsigned long long)gridDim.x * blockDim.x) >> 5) {
+        float acc = red_init(rtype);
+        for (unsigned s = lane; s < split; s += 32) acc = red_combine(rtype, acc, partial[o * split + s]);
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1) acc = red_combine(rtype, acc, __shfl_down_sync(0xffffffffu, acc, w));
+        if (lane == 0) out[o] = acc;
+    }
+}
+
 // second pass: out[o] = fold of partial[o*split .. o*split+split)
 __global__ void __launch_bounds__(256) k_red_final(const float *__restrict__ partial, float *__restrict__ out,
                                                    unsigned long long n_out, unsigned split, unsigned rtype) {
@@ -441,6 +541,8 @@ struct FastDesc {
     const char *name, *flat_name;   // kernel family for the launch statistics: general form, streamlined form
     bool  flat_shape;               // every leaf flat or one element, shape fit for the streamlined kernels
     bool  flat;                     // decided per launch: flat_shape and all pointers 16-byte aligned
+    bool  rows_shape, rows;         // same for the row kernels (contiguous rows, per-row constants)
+    const char *rows_name;
 };
 
 static bool build_fast(const GenDesc &H, FastDesc &F) {
@@ -538,7 +640,9 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
         }
         L.mode = single ? 2u : (flat ? 1u : 0u);
     }
-    D.vec = vec_ok ? 4u : 1u;
+    // elementwise dispatches whose innermost dim is even but not a multiple of 4 (2x2 pooling windows, rows padded
+    // to 66) still decode one coordinate set per pair of outputs
+    D.vec = vec_ok ? 4u : ((!H.has_reduce && D.dims[in] % 2 == 0) ? 2u : 1u);
     D.split = 1;
 
     // program; unary ops get b = a so they match the static chain table
@@ -567,8 +671,26 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
     for (unsigned i = 0; i < H.n_leaves; i++)
         if (!(D.leaf[i].mode == 2 || (D.leaf[i].mode == 1 && D.leaf[i].vec))) all_flat = false;
     F.flat_shape = false; F.flat = false;
-    F.flat_name = "";
-    if (!H.has_reduce) { F.strategy = 0; F.flat_shape = all_flat; F.flat_name = D.chain ? "ew_flat_static" : "ew_flat_interp"; F.name = D.chain ? (D.vec == 4 ? "ew_vec4_static" : "ew_scalar_static") : (D.vec == 4 ? "ew_vec4_interp" : "ew_scalar_interp"); return true; }
+    F.flat_name = ""; F.rows_name = ""; F.rows_shape = false; F.rows = false;
+    D.row_split = 1;
+    {   // row kernels: every leaf unmasked and either stride 1 (16-byte loadable) or stride 0 along the innermost dim
+        bool ok = D.vec == 4 && nd >= 2 && D.dims[in] >= 128 && (!H.has_reduce || D.is_red[in]);
+        for (unsigned i = 0; i < H.n_leaves && ok; i++) {
+            const FLeaf &L = D.leaf[i];
+            ok = L.masked == 0 && ((L.stride[in] == 1 && L.vec) || L.stride[in] == 0);
+        }
+        if (ok) {
+            unsigned long long om = 1, sm = 1;
+            for (int d = in - 1; d >= 0; d--) {
+                D.omul[d] = D.smul[d] = 0;
+                if (D.is_red[d]) { D.smul[d] = sm; sm *= D.dims[d]; } else { D.omul[d] = om; om *= D.dims[d]; }
+            }
+            if (sm <= 65535) { D.row_split = (unsigned)sm; F.rows_shape = true; }
+        }
+    }
+    if (!H.has_reduce && D.vec == 2) { F.strategy = 0; F.name = D.chain ? "ew_vec2_static" : "ew_vec2_interp"; return true; }
+    if (!H.has_reduce) { F.strategy = 0; F.flat_shape = all_flat; F.flat_name = D.chain ? "ew_flat_static" : "ew_flat_interp";
+        F.rows_name = D.chain ? "ew_rows_static" : "ew_rows_interp"; F.name = D.chain ? (D.vec == 4 ? "ew_vec4_static" : "ew_scalar_static") : (D.vec == 4 ? "ew_vec4_interp" : "ew_scalar_interp"); return true; }
     if (D.is_red[in]) {
         F.strategy = 1;
         const unsigned long long items = D.n_red / D.vec;
@@ -589,9 +711,12 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
             F.flat_name = F.group == 256 ? "reduce_rows_cta" : "reduce_rows_warp";
         }
         F.name = F.group == 256 ? (D.split > 1 ? "reduce_inner_cta_split" : "reduce_inner_cta") : (F.group == 32 ? "reduce_inner_warp" : "reduce_inner_thread");
+        F.rows_name = D.row_split > 1 ? "reduce_rows_split" : "reduce_rows";
+        if (F.flat_shape) F.rows_shape = false;            // the all-flat form is the cheaper special case
         return true;
     }
     F.strategy = 2;
+    F.rows_shape = false;
     D.vec = 1;
     const unsigned long long gx = (D.n_out + 31) / 32;
     if (gx > 0x7FFFFFFFull) return false;
@@ -627,10 +752,25 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
         else                k_rows<EV, 32><<<grid_for(D.n_out, 8, 8), 256, 0, g.stream>>>(D, out);
         return;
     }
+    if (F.rows) {
+        const unsigned long long R = D.numel / D.dims[D.rank - 1];
+        const bool cta = D.dims[D.rank - 1] / 4 >= 512;
+        const unsigned grid = cta ? (unsigned)(R < 0x7FFFFFFFull ? R : 0x7FFFFFFFull) : grid_for(R, 8, 8);
+        if (F.strategy == 0) {
+            if (cta) k_rowsx<EV, 256, false><<<grid, 256, 0, g.stream>>>(D, out);
+            else     k_rowsx<EV, 32, false><<<grid, 256, 0, g.stream>>>(D, out);
+        } else {
+            float *dst = D.split > 1 ? (float *)scratch_reserve(D.n_out * D.split * sizeof(float)) : out;
+            if (cta) k_rowsx<EV, 256, true><<<grid, 256, 0, g.stream>>>(D, dst);
+            else     k_rowsx<EV, 32, true><<<grid, 256, 0, g.stream>>>(D, dst);
+        }
+        return;
+    }
     if (F.strategy == 0) {
         const unsigned grid = grid_for(items, 256, 8);
-        if (D.vec == 4) k_ew<EV, 4><<<grid, 256, 0, g.stream>>>(D, out);
-        else            k_ew<EV, 1><<<grid, 256, 0, g.stream>>>(D, out);
+        if (D.vec == 4)      k_ew<EV, 4><<<grid, 256, 0, g.stream>>>(D, out);
+        else if (D.vec == 2) k_ew<EV, 2><<<grid, 256, 0, g.stream>>>(D, out);
+        else                 k_ew<EV, 1><<<grid, 256, 0, g.stream>>>(D, out);
         return;
     }
     float *dst = out;
@@ -670,8 +810,12 @@ bool launch_fast(Plan *p, const GenArgs &args) {
     float *out = (float *)args.out;
     if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return false;
     F.flat = F.flat_shape;
-    for (unsigned i = 0; i < D.prog.n_leaves; i++)
+    F.rows = F.rows_shape && !F.flat_shape;
+    for (unsigned i = 0; i < D.prog.n_leaves; i++) {
         if (D.leaf[i].mode == 1 && !D.leaf[i].vec) F.flat = false;
+        if (D.leaf[i].stride[D.rank - 1] == 1 && !D.leaf[i].vec) F.rows = false;
+    }
+    if (F.rows && F.strategy == 1) D.split = D.row_split;  // partial sums per output for the fold pass
     if (g.profile_level >= 2) {
         int w = snprintf(g.last_shape, sizeof g.last_shape, "dims=[");
         for (unsigned d = 0; d < D.rank; d++) w += snprintf(g.last_shape + w, sizeof g.last_shape - w, "%u%s%s", D.dims[d], D.is_red[d] ? "r" : "", d + 1 < D.rank ? "," : "");
@@ -701,9 +845,10 @@ bool launch_fast(Plan *p, const GenArgs &args) {
         case 16: launch_with<StaticEval<16>>(F, D, out); break;
         default: launch_with<InterpEval>(F, D, out); break;
     }
-    after_launch(F.flat ? F.flat_name : F.name);
+    after_launch(F.flat ? F.flat_name : (F.rows ? F.rows_name : F.name));
     if (F.strategy != 0 && D.split > 1) {
-        k_red_final<<<grid_for(D.n_out, 256, 4), 256, 0, g.stream>>>((const float *)g.scratch, out, D.n_out, D.split, D.rtype);
+        if (D.split >= 64) k_red_final_warp<<<grid_for(D.n_out, 8, 4), 256, 0, g.stream>>>((const float *)g.scratch, out, D.n_out, D.split, D.rtype);
+        else k_red_final<<<grid_for(D.n_out, 256, 4), 256, 0, g.stream>>>((const float *)g.scratch, out, D.n_out, D.split, D.rtype);
         after_launch("reduce_final");
     }
     return true;

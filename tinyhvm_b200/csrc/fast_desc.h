@@ -39,6 +39,8 @@ struct FDesc {
     unsigned split;              // CTAs sharing one output (two-pass reduce), >= 1
     unsigned chain;              // index into the static chain registry, or 0 = interpreted
     unsigned long long fstride[FR];  // row-major strides of the collapsed dims (flat position of a coordinate)
+    unsigned long long omul[FR], smul[FR];   // row kernels: contribution of an outer coordinate to the output index / to the partial-sum slot
+    unsigned row_split;              // row kernels: partial sums per output (product of the reduced outer dims), >= 1
     FLeaf    leaf[FL];
     FProg    prog;
 };

@@ -165,12 +165,17 @@ __device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, con
             const long long ko = klin ? (long long)k * klin : (long long)(in ? ktab[k] : 0);
             cp_async16(dst, in ? U.rowptr[i] + ko : P, in ? 16u : 0u);
         } else {
-#pragma unroll
-            for (uint32_t e = 0; e < 4; e++) {
-                const bool in = row_ok && k + e < K;
-                const long long ko = klin ? (long long)(k + e) * klin : (long long)(in ? ktab[k + e] : 0);
-                cp_async4(dst + 4u * e, in ? U.rowptr[i] + ko : P, in ? 4u : 0u);
-            }
+            // four 4-byte copies; the four k offsets come with one 16-byte load (k is a multiple of 4 and the
+            // table is padded with zeros to a multiple of 32 entries), nv = how many of them are inside K
+            const uint32_t nv = (row_ok && k < K) ? (K - k < 4u ? K - k : 4u) : 0u;
+            long long o0, o1, o2, o3;
+            if (klin) { o0 = (long long)k * klin; o1 = o0 + klin; o2 = o1 + klin; o3 = o2 + klin; }
+            else { const int4 t = *reinterpret_cast<const int4 *>(ktab + k); o0 = t.x; o1 = t.y; o2 = t.z; o3 = t.w; }
+            const float *rp = U.rowptr[i];
+            cp_async4(dst, nv > 0u ? rp + o0 : P, nv > 0u ? 4u : 0u);
+            cp_async4(dst + 4u, nv > 1u ? rp + o1 : P, nv > 1u ? 4u : 0u);
+            cp_async4(dst + 8u, nv > 2u ? rp + o2 : P, nv > 2u ? 4u : 0u);
+            cp_async4(dst + 12u, nv > 3u ? rp + o3 : P, nv > 3u ? 4u : 0u);
         }
     }
 }
