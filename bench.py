@@ -119,6 +119,60 @@ def gemm_section(be, stream, n: int, iters: int = 10):
     return res
 
 
+# ------------------------------------------------------------------ config 5's dominant kernels: the 64 -> 64 3x3 convolution
+def conv_dispatches(B: int, x, w, gy, Ci=64, Co=64, H=66, K=3):
+    """Forward and weight-gradient of a valid KxK convolution over a (pre-padded) [B,Ci,H,H] input, in the rank-8
+    MUL + SUM form the reference emits (src/nn/conv.c:390-478): full = [B,1,Co,OH,OW,Ci,K,K]."""
+    from tinyhvm_b200 import abi
+    from tinyhvm_b200.abi import MUL, SUM, Dispatch, Leaf
+    O = H - K + 1
+    full = [B, 1, Co, O, O, Ci, K, K]
+
+    def sv(strides):
+        v = abi.View()
+        v.shape = abi.make_shape(full)
+        for i, st in enumerate(strides):
+            v.strides[i] = st
+        return abi._finish(v)
+
+    vx = sv([Ci * H * H, 0, 0, H, 1, H * H, H, 1])
+    return {
+        "fprop": Dispatch([Leaf(x, vx), Leaf(w, sv([0, 0, Ci * K * K, 0, 0, K * K, K, 1]))], [(MUL, 0, 1)], full, [5, 6, 7], SUM),
+        "wgrad": Dispatch([Leaf(x, vx), Leaf(gy, sv([Co * O * O, 0, O * O, O, 1, 0, 0, 0]))], [(MUL, 0, 1)], full, [0, 3, 4], SUM),
+    }
+
+
+def conv_section(be, stream, B: int, iters: int = 5):
+    import torch
+    from tinyhvm_b200 import synth
+    seed = synth.SEED_BASE + 6
+    Ci = Co = 64; H = 66; K = 3; O = H - K + 1
+    x = synth.normal(seed, 0, B * Ci * H * H)
+    w = synth.normal(seed, 1, Co * Ci * K * K) / np.float32(np.sqrt(Ci * K * K))
+    gy = synth.normal(seed, 2, B * Co * O * O)
+    ds = conv_dispatches(B, x, w, gy)
+    ids = {k: be.upload(v) for k, v in (("x", x), ("w", w), ("gy", gy))}
+    leaf_ids = {"fprop": [ids["x"], ids["w"]], "wgrad": [ids["x"], ids["gy"]]}
+    res = {}
+    flops = 2.0 * B * Co * O * O * Ci * K * K
+    for name, d in ds.items():
+        out = be.alloc(d.out_numel * 4)
+        for _ in range(3):
+            be.dispatch_ids(out, leaf_ids[name], d)
+        be.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            be.dispatch_ids(out, leaf_ids[name], d)
+        e1.record(stream)
+        be.sync(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res[name] = {"ms": ms, "tflops": flops / ms / 1e9, "plan": be.last_plan()}
+    res["error"] = be.last_error()
+    be.reset(ids["x"] - 1)
+    return res
+
+
 # ------------------------------------------------------------------ configs 4 and 5: CNN training steps (trace replay)
 CNN = {"lenet": {"global_batch": 1024, "in_elems": 784, "classes": 10, "seed_off": 4},
        "vgg": {"global_batch": 512, "in_elems": 3 * 64 * 64, "classes": 100, "seed_off": 5}}
@@ -303,9 +357,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the chain (smaller only for profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--conv-batch", type=int, default=128, help="conv workload: images per launch of the 64->64 3x3 convolution at 64x64")
     ap.add_argument("--eager", action="store_true", help="lenet / vgg workloads: replay call by call instead of one CUDA graph launch per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "lenet", "vgg"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "lenet", "vgg"],
                     help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet / vgg = only the config-4 / config-5 training steps")
     ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
@@ -336,6 +391,14 @@ def main():
             print(json.dumps({"metric": "gemm_3xtf32_tflops", "unit": "TFLOP/s", "n_gpus": world, "dtype": "f32 (3xTF32 on tcgen05)",
                               "config": {"workload": f"cfg3 GEMMs, n={args.gemm_size}"}, "gemms": r,
                               "value": min(v["tflops"] for k, v in r.items() if isinstance(v, dict))}))
+        be.shutdown()
+        return
+    if args.workload == "conv":
+        r = conv_section(be, stream, args.conv_batch)
+        if rank == 0:
+            print(json.dumps({"metric": "conv_3xtf32_tflops", "unit": "TFLOP/s", "n_gpus": world, "dtype": "f32 (3xTF32 on tcgen05)",
+                              "config": {"workload": f"cfg5 conv 64->64 3x3 at 64x64, batch {args.conv_batch}: forward and weight gradient"},
+                              "convs": r, "value": min(v["tflops"] for v in r.values() if isinstance(v, dict))}))
         be.shutdown()
         return
     if args.workload in CNN:
