@@ -118,7 +118,7 @@ void after_launch(const char *plan) {
             THC_CUDA_OK(cudaEventSynchronize(prof_ev[1]));
             float ms = 0; THC_CUDA_OK(cudaEventElapsedTime(&ms, prof_ev[0], prof_ev[1]));
             s.ms += ms; prof_open = false;
-            if (g.profile_level >= 2 && ms > 0.1f) fprintf(stderr, "thvm_cuda slow launch: %-22s %8.3f ms  %s\n", plan, ms, g.last_shape);
+            if (g.profile_level >= 2 && (ms > 0.1f || g.profile_level >= 3)) fprintf(stderr, "thvm_cuda slow launch: %-22s %8.3f ms  %s\n", plan, ms, g.last_shape);
         }
     }
 }

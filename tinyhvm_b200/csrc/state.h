@@ -55,7 +55,7 @@ struct State {
     std::string  last_error;
     // profiling (THVM_PROFILE / profile_report)
     bool         profile = false;
-    int          profile_level = 0;   // THVM_PROFILE=2: also print every launch slower than 0.1 ms with its shape
+    int          profile_level = 0;   // THVM_PROFILE=2: also print every launch slower than 0.1 ms with its shape; 3: every launch
     char         last_shape[160] = {0};
 };
 
