@@ -152,7 +152,7 @@ __device__ __forceinline__ void make_units(UnitSet &U, const float *P, long long
     }
 }
 // issue the asynchronous copies of one operand k-block into its raw (= high part) tile;
-// rows past the matrix edge and k past K are zero-filled (source size 0).  `klin` != 0:
+// k past K is zero-filled (source size 0); rows past the matrix edge are skipped.  `klin` != 0:
 // the operand's k offset is k * klin (a single reduced dim), else it comes from `ktab`.
 __device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, const int32_t *__restrict__ ktab, long long klin,
                                            uint32_t k0, uint32_t K, uint32_t kvec, uint32_t tile) {
@@ -160,6 +160,7 @@ __device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, con
     for (int i = 0; i < UNITS; i++) {
         const uint32_t k = k0 + U.kcol[i], dst = tile + U.soff[i];
         const bool row_ok = (U.live >> i) & 1u;
+        if (!row_ok) continue;                 // rows past the edge: their products land in accumulator rows / columns nobody stores
         if (kvec) {
             const bool in = row_ok && k < K;
             const long long ko = klin ? (long long)k * klin : (long long)(in ? ktab[k] : 0);
@@ -197,6 +198,7 @@ __device__ __forceinline__ void prefetch_tile(const UnitSet &U, long long klin, 
 __device__ __forceinline__ void split_tile(const UnitSet &U, uint32_t raw_tile, uint32_t lo_tile) {
 #pragma unroll
     for (int i = 0; i < UNITS; i++) {
+        if (!((U.live >> i) & 1u)) continue;
         uint32_t x0, x1, x2, x3;
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(raw_tile + U.soff[i]) : "memory");
         st_shared_v4(lo_tile + U.soff[i], tf32_low(x0), tf32_low(x1), tf32_low(x2), tf32_low(x3));
