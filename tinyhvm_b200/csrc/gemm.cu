@@ -42,7 +42,7 @@ constexpr int GEMM_THREADS = NPROD + 32;            // + 1 MMA warp
 constexpr int MMA_WARP = PROD_WARPS;
 constexpr int TMEM_COLS = 128;
 constexpr int PREFETCH_AHEAD = 8;                   // k-blocks between an L2 prefetch and its cp.async
-constexpr int LOOKAHEAD = 3;                        // k-blocks of cp.async in flight ahead of the split pass
+constexpr int LOOKAHEAD = 2;                        // k-blocks of cp.async in flight ahead of the split pass
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 enum : int { ERR_GEMM_TIMEOUT = 8 };
 
@@ -492,30 +492,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) k_g
         auto issue = [&](uint32_t kb) {
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, k0 = (kb_lo + kb) * BK;
             issue_tile(UA, G.A, G.ka, G.a_klin, k0, G.K, G.a_kvec, st);
-            issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + TILE_BYTES);
+            if (G.debug_mode != 6) issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + TILE_BYTES);
         };
+        const uint32_t dbg = G.debug_mode;                               // timing experiments: 1 MMAs only, 2 no MMAs, 3 no copies, 4 no low-part pass
         for (uint32_t kb = 0; kb < (uint32_t)LOOKAHEAD; kb++) {
-            if (kb < nkb) issue(kb);
+            if (kb < nkb && dbg != 1 && dbg != 3) issue(kb);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-            asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
+            if (dbg != 5) asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
             if (kb >= (uint32_t)LO_STAGES) {
                 const uint32_t prev = kb - LO_STAGES;
                 ok = mbar_wait(smem_u32(&S.empty[prev % STAGES]), (prev / STAGES) & 1u, abort_flag);
                 if (!ok) break;
             }
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, lo = tiles_s + LO_BASE + (kb % LO_STAGES) * STAGE_BYTES;
-            split_tile(UA, st, lo);
-            split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (dbg != 1 && dbg != 4) {
+                split_tile(UA, st, lo);
+                split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
+            }
+            if (dbg != 7) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&S.full[kb % STAGES]), 0));   // one arrival per warp, on the first CTA's barrier
             const uint32_t nxt = kb + LOOKAHEAD;
             if (nxt < nkb) {
                 const uint32_t use = nxt / STAGES;
                 if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[nxt % STAGES]), (use - 1) & 1u, abort_flag);
-                if (ok) issue(nxt);
+                if (ok && dbg != 1 && dbg != 3) issue(nxt);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -575,7 +578,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) k_g
                 const uint64_t a_hi = umma_desc(st), b_hi = umma_desc(st + TILE_BYTES);
                 const uint64_t a_lo = umma_desc(lo), b_lo = umma_desc(lo + TILE_BYTES);
 #pragma unroll
-                for (uint32_t ks = 0; ks < (uint32_t)(BK / 8); ks++) {
+                for (uint32_t ks = 0; ks < (G.debug_mode == 2 ? 0u : (uint32_t)(BK / 8)); ks++) {
                     const uint64_t adv = (uint64_t)(ks * 2u);
                     umma2_tf32(tmem, a_lo + adv, b_hi + adv, idesc, (kb | ks) ? 1u : 0u);
                     umma2_tf32(tmem, a_hi + adv, b_lo + adv, idesc, 1u);
