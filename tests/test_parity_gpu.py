@@ -217,6 +217,8 @@ def contraction_cases():
         cases.mm_case(rng, 300, 96, 300), cases.mm_case(rng, 600, 64, 100, ta=True), cases.mm_case(rng, 512, 70, 40, tb=True),
         cases.mm_case(rng, 256, 2100, 256), cases.mm_case(rng, 40, 130, 700), cases.mm_case(rng, 1024, 256, 512),
         cases.conv_fprop_case(rng, 8, 16, 18, 18, 64, 3), cases.conv_wgrad_case(rng, 4, 32, 12, 12, 16, 3),
+        # convolutions whose re-laid operands arrive by tile loads: 32 and 64 input channels, output widths 16 and 32
+        cases.conv_fprop_case(rng, 2, 32, 18, 18, 64, 3), cases.conv_fprop_case(rng, 1, 64, 34, 34, 32, 3),
         # thin shapes on the CUDA-core kernels: many rows x few columns, and few outputs x very long K
         cases.conv_fprop_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 5000, 40, 12), cases.mm_case(rng, 4100, 300, 27),
         cases.conv_wgrad_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 10, 6000, 20), cases.mm_case(rng, 16, 9000, 150, ta=True),
@@ -236,4 +238,5 @@ def test_contraction_kernel(cuda, oracle):
     assert all(p.startswith("gemm") or p.startswith("contract_skinny") for p in plans), plans
     assert sum(p == "contract_skinny_rows" for p in plans) >= 3, plans
     assert any("splitk" in p for p in plans), plans
-    assert sum(p.startswith("gemm_pair") for p in plans) >= 6, plans
+    assert sum(p.startswith("gemm_pair") or p.startswith("gemm_tma") for p in plans) >= 6, plans
+    assert sum(p.startswith("gemm_tma") for p in plans) >= 4, plans
