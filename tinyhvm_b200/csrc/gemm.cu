@@ -9,17 +9,21 @@
 // over expanded pool views (src/ctx/init.c:555-582, src/nn/conv.c:390-478) and
 // its CPU backend evaluates one product at a time (src/backend/cpu/dispatch.c:169-218).
 //
-// One CTA computes one 128x128 tile of C.  Warps 0..PROD_WARPS-1 are producers: they gather
-// the 128x32 A and B k-blocks from global memory through the separable offsets
-// (implicit im2col: no expanded copy of the input ever exists), split each value
-// and store hi and lo tiles into shared memory in the K-major 128-byte-swizzled
-// layout the MMA reads; two groups of four warps alternate k-blocks so one
-// group's global loads overlap the other's stores.  The last warp issues the MMAs (one
-// elected lane): per k-block 4 k-steps x 3 products, then tcgen05.commit hands
-// the stage back.  After the last k-block all producer warps read the
-// accumulators back with tcgen05.ld and store C through its separable offsets.
-// Stages are guarded by mbarriers; every wait is bounded and raises a status
-// bit instead of hanging.
+// Kernels in this translation unit, chosen per plan by the recogniser (gemm_host.inc):
+//   k_gemm_pair_tma      (gemm_tma.inc) CTA pair, 256-row tiles, operand k-blocks by TMA tile loads: matrices whose
+//                        operands are (or are transposed into) k-contiguous form, NCHW convolutions over
+//                        channels-last re-laid operands;
+//   k_gemm_pair_3xtf32   CTA pair, operands gathered with cp.async through separable offsets (implicit im2col:
+//                        weight gradients, operands with odd pitches, K not a multiple of 4);
+//   k_gemm_3xtf32        single CTA, 128x128 tile, same gather, for outputs with fewer than 256 rows;
+//   k_skinny_rows / _k   (gemm_skinny.inc) CUDA-core kernels for shapes too thin for a tensor-core tile.
+// Common structure of the tensor-core kernels: sixteen producer warps put 128x32 k-blocks of A and B into
+// shared memory in the K-major 128-byte-swizzled layout the MMA reads.  The raw f32 tile is the high part
+// as it stands (the tf32 MMA ignores the low 13 mantissa bits); a pass over the tile writes the low parts.
+// One elected lane of the MMA warp issues, per k-block, 4 k-steps x 3 products and hands the stage back
+// with tcgen05.commit.  After the last k-block the producer warps read the accumulators back with
+// tcgen05.ld and store C through its separable offsets.  Stages are guarded by mbarriers; every wait is
+// bounded and raises a status bit instead of hanging.
 #include <string.h>
 #include <vector>
 #include "device_common.cuh"
