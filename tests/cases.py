@@ -119,6 +119,22 @@ def maxpool_case(rng, B, Cc, H, W, ties=False):
     return Dispatch([Leaf(x, abi._finish(v))], [], full, [4, 5], RMAX, name=f"maxpool_b{B}c{Cc}h{H}w{W}")
 
 
+def maxpool_bwd_case(rng, B, Cc, H, W, ties=False):
+    """Mask-form gradient of the 2x2 pool in window layout: g * (1 - (max > x)) over [B,C,OH,OW,2,2]."""
+    from tinyhvm_b200.abi import CMP, SUB
+    OH, OW = H // 2, W // 2
+    x = _f32(rng, B * Cc * H * W)
+    if ties:
+        x = np.round(x)
+    mx = x.reshape(B, Cc, OH, 2, OW, 2).max(axis=(3, 5)).ravel().astype(np.float32)
+    g = _f32(rng, B * Cc * OH * OW)
+    full = [B, Cc, OH, OW, 2, 2]
+    vx = strided(full, [Cc * H * W, H * W, 2 * W, 2, W, 1])
+    vp = strided(full, [Cc * OH * OW, OH * OW, OW, 1, 0, 0])
+    return Dispatch([Leaf(g, vp), scalar_leaf(1.0, 6), Leaf(mx, vp), Leaf(x, vx)], [(CMP, 2, 3), (SUB, 1, 4), (MUL, 0, 5)], full,
+                    name=f"maxpool_bwd_b{B}c{Cc}h{H}w{W}")
+
+
 def bn_stats_case(rng, B, Cc, H, W):
     return Dispatch([dense(rng, [B, Cc, H, W])], [], [B, Cc, H, W], [0, 2, 3], SUM, name=f"bn_stats_b{B}c{Cc}h{H}w{W}")
 

@@ -93,3 +93,19 @@ def test_argmax_rows_matches_oracle(cuda, oracle, rows, cols):
     assert cuda.lib.thvm_cuda_argmax_rows(bo, bx, rows, cols) == 0, cuda.last_error()
     assert np.array_equal(cuda.read(bo, np.uint32, rows), want)
     cuda.reset(0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape,ties", [((4, 6, 28, 28), False), ((2, 3, 8, 8), True), ((3, 5, 10, 10), True), ((1, 2, 6, 14), False)])
+def test_maxpool_backward_dispatch_is_bit_exact(cuda, oracle, shape, ties):
+    """The mask-form pool gradient (src/interact/grad.c:406-425) runs on the pooling-backward kernel: same bits as
+    the oracle's op-by-op evaluation, ties included (every maximum passes the gradient)."""
+    import cases
+    d = cases.maxpool_bwd_case(np.random.default_rng(sum(shape)), *shape, ties=ties)
+    cuda.reset(0)
+    got = cuda.run(d)
+    assert cuda.last_plan() == "pool2x2_backward", cuda.last_plan()
+    want = oracle.run(d)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert cuda.last_error() == ""
+    cuda.reset(0)

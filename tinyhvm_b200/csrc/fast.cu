@@ -731,7 +731,7 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
 
 void classify_plan(Plan *p) {
     if (try_contraction(p)) return;
-    if (try_pool2x2(p)) return;
+    if (try_pool2x2(p) || try_pool2x2_bwd(p)) return;
     FastDesc *F = new FastDesc();
     if (build_fast(p->host, *F)) { p->fast = (struct FastDesc *)F; p->kind = F->strategy == 0 ? PLAN_EW : PLAN_REDUCE; }
     else { delete F; p->fast = nullptr; p->kind = PLAN_GENERIC; }
@@ -754,7 +754,8 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
     }
     if (F.rows) {
         const unsigned long long R = D.numel / D.dims[D.rank - 1];
-        const bool cta = D.dims[D.rank - 1] / 4 >= 512;
+        static const unsigned rows_cta_min = getenv("THVM_ROWS_CTA_MIN") ? (unsigned)atoi(getenv("THVM_ROWS_CTA_MIN")) : 2048u;
+        const bool cta = D.dims[D.rank - 1] / 4 >= rows_cta_min;
         const unsigned grid = cta ? (unsigned)(R < 0x7FFFFFFFull ? R : 0x7FFFFFFFull) : grid_for(R, 8, 8);
         if (F.strategy == 0) {
             if (cta) k_rowsx<EV, 256, false><<<grid, 256, 0, g.stream>>>(D, out);
@@ -799,6 +800,7 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
 bool launch_fast(Plan *p, const GenArgs &args) {
     if (p->kind == PLAN_CONTRACT) return launch_contraction(p, args);
     if (p->kind == PLAN_POOL) return launch_pool2x2(p, args);
+    if (p->kind == PLAN_POOL_BWD) return launch_pool2x2_bwd(p, args);
     FastDesc &F = *(FastDesc *)p->fast;
     FDesc D = F.d;
     for (unsigned i = 0; i < D.prog.n_leaves; i++) {

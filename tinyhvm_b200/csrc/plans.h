@@ -11,6 +11,7 @@ enum PlanKind : int {
     PLAN_REDUCE,        // collapsed-dims reduce (reduce.cu)
     PLAN_CONTRACT,      // SUM(MUL(a,b)) with separable operands -> GEMM (gemm.cu)
     PLAN_POOL,          // RMAX over the 2x2 windows of contiguous planes -> pooling kernel (uop.cu)
+    PLAN_POOL_BWD,      // the mask-form gradient of that pool -> pooling backward kernel (uop.cu)
 };
 
 struct FastDesc;        // family-specific, defined in fast_desc.h
@@ -25,7 +26,7 @@ struct Plan {
     void      *contract = nullptr;      // owned (gemm.cu); set for PLAN_CONTRACT
     unsigned long long pool_planes = 0; // PLAN_POOL: contiguous [planes, pool_h, pool_w] input starting at element pool_off
     uint32_t   pool_h = 0, pool_w = 0;
-    long long  pool_off = 0;
+    long long  pool_off = 0, pool_g_off = 0, pool_m_off = 0, pool_one_off = 0;
 };
 
 // Decide the family for a freshly built plan (sets kind / fast).
@@ -40,5 +41,7 @@ void free_contraction(Plan *p);
 // RMAX over 2x2 stride-2 windows of contiguous planes -> pooling kernel (uop.cu)
 bool try_pool2x2(Plan *p);
 bool launch_pool2x2(Plan *p, const GenArgs &args);
+bool try_pool2x2_bwd(Plan *p);
+bool launch_pool2x2_bwd(Plan *p, const GenArgs &args);
 
 }  // namespace thc

@@ -216,6 +216,106 @@ bool try_pool2x2(Plan *p) {
     return true;
 }
 
+// ---- the max-pool backward dispatch, out[.., oy, ox, i, j] = g[.., oy, ox] * (one - (max[.., oy, ox] > x[.., 2oy+i, 2ox+j])) ----
+// (the mask form of the reference's RMAX gradient rule, src/interact/grad.c:406-425: every element equal to the
+// maximum passes the gradient).  Output in window layout [planes, OH, OW, 2, 2], contiguous.
+__global__ void __launch_bounds__(256) k_maxpool2x2_bwd(const float *__restrict__ g, const float *__restrict__ one, const float *__restrict__ mx,
+                                                        const float *__restrict__ x, float *__restrict__ out,
+                                                        unsigned long long planes, unsigned H, unsigned W, unsigned vec) {
+    const unsigned OH = H / 2, OW = W / 2;
+    const unsigned per_row = vec ? OW / 2 : OW;
+    const unsigned long long items = planes * OH * per_row;
+    const float o1 = one[0];
+    for (unsigned long long it = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; it < items;
+         it += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned c = (unsigned)(it % per_row);
+        const unsigned long long rowi = it / per_row;                // plane * OH + oy
+        const unsigned oy = (unsigned)(rowi % OH);
+        const unsigned long long plane = rowi / OH;
+        const float *r0 = x + (plane * H + 2ull * oy) * W;
+        const float *r1 = r0 + W;
+        const unsigned long long o = rowi * OW;
+        auto f = [&](float gg, float m, float v) { return __fmul_rn(gg, __fsub_rn(o1, m > v ? 1.0f : 0.0f)); };
+        if (vec) {
+            const float4 a = *reinterpret_cast<const float4 *>(r0 + 4u * c), b = *reinterpret_cast<const float4 *>(r1 + 4u * c);
+            const float2 gg = *reinterpret_cast<const float2 *>(g + o + 2u * c), mm = *reinterpret_cast<const float2 *>(mx + o + 2u * c);
+            float4 *dst = reinterpret_cast<float4 *>(out + (o + 2u * c) * 4ull);
+            dst[0] = make_float4(f(gg.x, mm.x, a.x), f(gg.x, mm.x, a.y), f(gg.x, mm.x, b.x), f(gg.x, mm.x, b.y));
+            dst[1] = make_float4(f(gg.y, mm.y, a.z), f(gg.y, mm.y, a.w), f(gg.y, mm.y, b.z), f(gg.y, mm.y, b.w));
+        } else {
+            const float gg = g[o + c], m = mx[o + c];
+            float4 *dst = reinterpret_cast<float4 *>(out + (o + c) * 4ull);
+            dst[0] = make_float4(f(gg, m, r0[2u * c]), f(gg, m, r0[2u * c + 1]), f(gg, m, r1[2u * c]), f(gg, m, r1[2u * c + 1]));
+        }
+    }
+}
+
+static bool window_view(const GenDesc &H, const DLeaf &L, unsigned long long &planes, unsigned long long &Hh, unsigned long long &W) {
+    const int r = (int)H.rank;
+    if (L.dtype != THC_F32 || L.tracker >= 0 || L.v.has_mask || L.v.n_cm || r < 4 || (int)L.v.rank != r) return false;
+    for (int d = 0; d < r; d++) if (L.v.dims[d] != H.full_dims[d]) return false;
+    if (H.full_dims[r - 1] != 2 || H.full_dims[r - 2] != 2) return false;
+    const unsigned long long OW = H.full_dims[r - 3], OH = H.full_dims[r - 4];
+    W = 2 * OW; Hh = 2 * OH;
+    if (L.v.strides[r - 1] != 1 || L.v.strides[r - 2] != (long long)W || L.v.strides[r - 3] != 2 || L.v.strides[r - 4] != (long long)(2 * W)) return false;
+    planes = 1;
+    unsigned long long want = Hh * W;
+    for (int d = r - 5; d >= 0; d--) {
+        if (H.full_dims[d] != 1 && (unsigned long long)L.v.strides[d] != want) return false;
+        planes *= H.full_dims[d]; want *= H.full_dims[d];
+    }
+    return L.v.offset >= 0 && Hh <= 0xFFFFFFFFull && W <= 0xFFFFFFFFull;
+}
+// a [planes, OH, OW] tensor broadcast over the 2x2 window dims
+static bool pooled_view(const GenDesc &H, const DLeaf &L) {
+    const int r = (int)H.rank;
+    if (L.dtype != THC_F32 || L.tracker >= 0 || L.v.has_mask || L.v.n_cm || (int)L.v.rank != r) return false;
+    for (int d = 0; d < r; d++) if (L.v.dims[d] != H.full_dims[d]) return false;
+    const unsigned long long OW = H.full_dims[r - 3], OH = H.full_dims[r - 4];
+    if (L.v.strides[r - 1] != 0 || L.v.strides[r - 2] != 0 || L.v.strides[r - 3] != 1 || L.v.strides[r - 4] != (long long)OW) return false;
+    unsigned long long want = OH * OW;
+    for (int d = r - 5; d >= 0; d--) {
+        if (H.full_dims[d] != 1 && (unsigned long long)L.v.strides[d] != want) return false;
+        want *= H.full_dims[d];
+    }
+    return L.v.offset >= 0;
+}
+
+bool try_pool2x2_bwd(Plan *p) {
+    const GenDesc &H = p->host;
+    if (H.has_reduce || H.n_leaves != 4 || H.n_ops != 3 || H.post_start || H.out_dtype != THC_F32) return false;
+    const thc_fused_op_t *o = H.ops;
+    if (!(o[0].uop == THC_CMP && o[0].arg_a == 2 && o[0].arg_b == 3 && o[1].uop == THC_SUB && o[1].arg_a == 1 && o[1].arg_b == 4 &&
+          o[2].uop == THC_MUL && o[2].arg_a == 0 && o[2].arg_b == 5)) return false;
+    unsigned long long planes, Hh, W;
+    if (!window_view(H, H.leaves[3], planes, Hh, W) || !pooled_view(H, H.leaves[0]) || !pooled_view(H, H.leaves[2])) return false;
+    const DLeaf &S1 = H.leaves[1];
+    if (S1.dtype != THC_F32 || S1.tracker >= 0 || S1.v.has_mask || S1.v.offset < 0) return false;
+    for (unsigned d = 0; d < S1.v.rank; d++) if (S1.v.dims[d] != 1 && S1.v.strides[d] != 0) return false;
+    p->pool_planes = planes; p->pool_h = (uint32_t)Hh; p->pool_w = (uint32_t)W; p->pool_off = H.leaves[3].v.offset;
+    p->pool_g_off = H.leaves[0].v.offset; p->pool_one_off = S1.v.offset; p->pool_m_off = H.leaves[2].v.offset;
+    p->kind = PLAN_POOL_BWD;
+    return true;
+}
+
+bool launch_pool2x2_bwd(Plan *p, const GenArgs &args) {
+    const unsigned long long in_n = p->pool_planes * p->pool_h * p->pool_w, out_n = in_n / 4;
+    if ((unsigned long long)p->pool_off + in_n > args.cap[3] || (unsigned long long)p->pool_g_off + out_n > args.cap[0] ||
+        (unsigned long long)p->pool_m_off + out_n > args.cap[2] || (unsigned long long)p->pool_one_off >= args.cap[1])
+        return false;
+    const float *gr = (const float *)args.leaf[0] + p->pool_g_off, *one = (const float *)args.leaf[1] + p->pool_one_off;
+    const float *mx = (const float *)args.leaf[2] + p->pool_m_off, *x = (const float *)args.leaf[3] + p->pool_off;
+    if (reinterpret_cast<uintptr_t>(args.out) & 15u) return false;
+    const unsigned vec = (p->pool_w % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(gr) & 7u) == 0 &&
+                          (reinterpret_cast<uintptr_t>(mx) & 7u) == 0) ? 1u : 0u;
+    const uint64_t items = p->pool_planes * (p->pool_h / 2) * (vec ? p->pool_w / 4 : p->pool_w / 2);
+    if (g.profile_level >= 2) snprintf(g.last_shape, sizeof g.last_shape, "planes=%llu H=%u W=%u vec=%u", p->pool_planes, p->pool_h, p->pool_w, vec);
+    profile_begin();
+    k_maxpool2x2_bwd<<<grid_for(items, 256, 8), 256, 0, g.stream>>>(gr, one, mx, x, (float *)args.out, p->pool_planes, p->pool_h, p->pool_w, vec);
+    after_launch("pool2x2_backward");
+    return true;
+}
+
 bool launch_pool2x2(Plan *p, const GenArgs &args) {
     const unsigned long long in_n = p->pool_planes * p->pool_h * p->pool_w;
     if ((unsigned long long)p->pool_off + in_n > args.cap[0]) return false;         // would leave the buffer: the checked generic kernel runs
