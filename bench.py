@@ -491,12 +491,24 @@ def main():
     # ---- end to end with host buffers through the same C ABI
     e2e_steps = max(3, min(args.steps, 5))
 
+    # The rows go through in slices: while slice i is uploaded (buf_write waits for its DMA) and computed, the results of
+    # slice i-1 travel back on the library's copy stream (buf_read_async), so the two PCIe directions overlap.
+    n_slices = 8 if rows % 8 == 0 and rows >= 64 else 1
+    srows = rows // n_slices
+    s_fwd, s_bwd = chain_dispatches(srows, COLS, [x[: srows * COLS] for x in arrays])
+    s_ids = [[be.alloc(srows * COLS * 4) for _ in range(3)] for _ in range(n_slices)]
+    s_out = [(be.alloc(srows * 4), be.alloc(srows * COLS * 4)) for _ in range(n_slices)]
+
     def e2e_step():
-        for i, a in zip(ids, arrays):
-            lib.thvm_cuda_buf_write(i, a.ctypes.data, a.nbytes)
-        step()
-        lib.thvm_cuda_buf_read_nosync(g_id, g_host.data_ptr(), g_host.numel() * 4)
-        lib.thvm_cuda_buf_read(y_id, y_host.data_ptr(), y_host.numel() * 4)
+        for s in range(n_slices):
+            lo = s * srows * COLS
+            for i, a in zip(s_ids[s], arrays):
+                lib.thvm_cuda_buf_write(i, a[lo: lo + srows * COLS].ctypes.data, srows * COLS * 4)
+            be.dispatch_ids(s_out[s][0], s_ids[s], s_fwd)
+            be.dispatch_ids(s_out[s][1], s_ids[s] + [zero_id], s_bwd)
+            lib.thvm_cuda_buf_read_async(s_out[s][1], g_host.data_ptr() + lo * 4, srows * COLS * 4)
+            lib.thvm_cuda_buf_read_async(s_out[s][0], y_host.data_ptr() + s * srows * 4, srows * 4)
+        lib.thvm_cuda_sync()
 
     e2e_step()
     barrier()

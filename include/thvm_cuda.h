@@ -174,6 +174,9 @@ void     thvm_cuda_dispatch_uop_kernel(uint32_t out_buf, const uint32_t *leaf_bu
 void     thvm_cuda_contiguify(uint32_t dst_buf, uint32_t numel, uint32_t src_buf, const thc_view_t *src_view);
 void     thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes);
 void     thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes);
+/* Extra, no vtable slot: asynchronous read-back on a copy stream of the library's own, ordered after the work
+ * already queued; `out` (pinned memory) is valid after thvm_cuda_sync().  Overlaps later uploads and kernels. */
+void     thvm_cuda_buf_read_async(uint32_t id, void *out, uint64_t bytes);
 
 /* In-place Adam — src/tinyhvm.h:1033-1035 (math: src/shaders.metal:406-420). */
 void     thvm_cuda_adam_step(uint32_t param, uint32_t grad, uint32_t m, uint32_t v,

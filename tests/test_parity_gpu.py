@@ -244,3 +244,32 @@ def test_contraction_kernel(cuda, oracle):
     assert any("splitk" in p for p in plans), plans
     assert sum(p.startswith("gemm_pair") or p.startswith("gemm_tma") for p in plans) >= 6, plans
     assert sum(p.startswith("gemm_tma") for p in plans) >= 4, plans
+
+
+def test_read_back_variants(cuda):
+    """buf_read_nosync hands back valid bytes on return (the reference reads metadata through it, src/interact/_.c:8-11),
+    for host-written and for device-written buffers; buf_read_async delivers after thvm_cuda_sync and the library keeps a
+    later overwrite of the buffer behind the copy."""
+    import ctypes as C
+    lib = cuda.lib
+    cuda.reset(0)
+    small = np.arange(8, dtype=np.float32)
+    big = np.random.default_rng(3).standard_normal(1 << 20).astype(np.float32)
+    bs, bb = cuda.upload(small), cuda.upload(big)
+    out_s, out_b = np.zeros_like(small), np.zeros_like(big)
+    lib.thvm_cuda_buf_read_nosync(bs, out_s.ctypes.data, out_s.nbytes)
+    lib.thvm_cuda_buf_read_nosync(bb, out_b.ctypes.data, out_b.nbytes)
+    assert np.array_equal(out_s, small) and np.array_equal(out_b, big)
+    dst = cuda.alloc(big.nbytes)
+    lib.thvm_cuda_buf_copy(dst, bb, big.nbytes)                       # device-written
+    out_b[:] = 0
+    lib.thvm_cuda_buf_read_nosync(dst, out_b.ctypes.data, out_b.nbytes)
+    assert np.array_equal(out_b, big)
+    out_a = np.zeros_like(big)
+    lib.thvm_cuda_buf_read_async(dst, out_a.ctypes.data, out_a.nbytes)
+    cuda.write(dst, np.zeros_like(big))                               # must not overtake the read-back
+    lib.thvm_cuda_sync()
+    assert np.array_equal(out_a, big)
+    assert np.array_equal(cuda.read(dst, np.float32, big.size), np.zeros_like(big))
+    cuda.reset(0)
+    assert cuda.last_error() == ""

@@ -48,6 +48,7 @@ SYMBOLS = {
     "thvm_cuda_contiguify": (None, [_u32, _u32, _u32, _PV]),
     "thvm_cuda_buf_copy": (None, [_u32, _u32, _u64]),
     "thvm_cuda_buf_read_nosync": (None, [_u32, _vp, _u64]),
+    "thvm_cuda_buf_read_async": (None, [_u32, _vp, _u64]),
     "thvm_cuda_adam_step": (None, [_u32, _u32, _u32, _u32] + [C.c_float] * 6 + [_u32]),
     "thvm_cuda_pool_reset": (None, [_u32]),
     "thvm_cuda_pool_set_persistent": (None, [_u32]),

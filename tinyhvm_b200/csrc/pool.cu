@@ -54,9 +54,11 @@ Buf &buf_live(uint32_t id, const char *who) {
 }
 
 static uint8_t *ring_take(uint64_t bytes);
+void fence_copy(Buf &b);
 
 Buf &buf_checked(uint32_t id, const char *who) {
     Buf &b = buf_live(id, who);
+    fence_copy(b);                                  // whatever comes next on the main stream stays behind a running read-back of b
     if (!b.ptr) {                                   // host-only so far: attach device memory now
         uint64_t sz = (b.bytes + 15) & ~15ull;
         if (sz == 0) sz = 16;
@@ -82,8 +84,15 @@ Buf &buf_checked(uint32_t id, const char *who) {
     return b;
 }
 
+void fence_copy(Buf &b) {
+    if (!b.copy_pending) return;
+    THC_CUDA_OK(cudaStreamWaitEvent(g.stream, g.copy_done, 0));    // copy_done follows the latest asynchronous read-back
+    b.copy_pending = false;
+}
+
 Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written) {
     Buf &b = buf_live(id, who);
+    fence_copy(b);
     if (b.ptr && b.zero_pending && bytes_written >= b.bytes) b.zero_pending = false;
     return buf_checked(id, who);
 }
@@ -196,6 +205,9 @@ int thvm_cuda_init(void) {
     g.device = dev;
     g.sm_count = prop.multiProcessorCount;
     THC_CUDA_OK(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+    THC_CUDA_OK(cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking));
+    THC_CUDA_OK(cudaEventCreateWithFlags(&g.copy_after, cudaEventDisableTiming));
+    THC_CUDA_OK(cudaEventCreateWithFlags(&g.copy_done, cudaEventDisableTiming));
     cudaMemPool_t mp;
     THC_CUDA_OK(cudaDeviceGetDefaultMemPool(&mp, dev));
     uint64_t keep_all = UINT64_MAX;
@@ -220,6 +232,7 @@ int thvm_cuda_init(void) {
 
 static void release(uint32_t id) {
     Buf &b = g.bufs[id];
+    fence_copy(b);
     if (b.ptr && g.cap && id < capture_first_id())
         capture_fail("the captured step frees a buffer that was allocated before the capture began");
     if (b.ptr) {
@@ -246,6 +259,9 @@ void thvm_cuda_shutdown(void) {
     cudaFree(g.dev_status); g.dev_status = nullptr;
     cudaFreeHost(g.ring); g.ring = nullptr;
     for (int i = 0; i < 2; i++) { cudaEventDestroy(g.ring_half[i]); g.ring_half[i] = nullptr; }
+    cudaStreamSynchronize(g.copy_stream);
+    cudaEventDestroy(g.copy_after); cudaEventDestroy(g.copy_done); g.copy_after = g.copy_done = nullptr;
+    cudaStreamDestroy(g.copy_stream); g.copy_stream = nullptr;
     cudaStreamDestroy(g.stream); g.stream = nullptr;
     g.count = 1;
     g.ready = false;
@@ -307,6 +323,7 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
     if (bytes == 0) return;
     if (b.shadow) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
     if (!b.ptr) return;                            // host-only buffer: uploaded if and when the device needs it
+    fence_copy(b);
     if (b.zero_pending) {
         if (bytes < b.bytes) THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
         b.zero_pending = false;
@@ -337,9 +354,26 @@ static void read_impl(uint32_t id, void *out, uint64_t bytes, bool sync) {
     if (sync) check_device_status("buf_read");                // drains the stream
 }
 void thvm_cuda_buf_read(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, true); }
-// The copy is still stream-ordered after the kernels that produced the data;
-// only the final wait is left to the caller (thvm_cuda_sync).
-void thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, false); }
+// The vtable's buf_read_nosync serves META_READ (src/interact/_.c:8-11): small metadata the host wrote itself, read
+// back "without a GPU flush", and the caller uses the bytes as soon as the call returns.  Host-written buffers of up
+// to 256 bytes come from their host shadow without touching the device; anything else is read like buf_read.
+void thvm_cuda_buf_read_nosync(uint32_t id, void *out, uint64_t bytes) { read_impl(id, out, bytes, true); }
+// Asynchronous read-back (no vtable slot): the copy is ordered after the work already queued on the main stream and
+// runs on a copy stream of its own, so it overlaps later uploads and kernels; `out` (pinned memory keeps it truly
+// asynchronous) holds the data after thvm_cuda_sync().  The library keeps later writes to and frees of the same
+// buffer behind the copy.
+void thvm_cuda_buf_read_async(uint32_t id, void *out, uint64_t bytes) {
+    Buf &b = buf_live(id, "buf_read_async");
+    uint64_t n = bytes < b.bytes ? bytes : b.bytes;
+    if (bytes > n) memset((uint8_t *)out + n, 0, bytes - n);
+    if (n == 0) return;
+    if ((b.shadow && b.shadow_valid) || !b.ptr || b.zero_pending || g.cap) { read_impl(id, out, bytes, false); return; }
+    THC_CUDA_OK(cudaEventRecord(g.copy_after, g.stream));
+    THC_CUDA_OK(cudaStreamWaitEvent(g.copy_stream, g.copy_after, 0));
+    THC_CUDA_OK(cudaMemcpyAsync(out, b.ptr, n, cudaMemcpyDeviceToHost, g.copy_stream));
+    THC_CUDA_OK(cudaEventRecord(g.copy_done, g.copy_stream));
+    b.copy_pending = true;
+}
 
 void thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes) {
     Buf &dl = buf_live(dst_buf, "buf_copy(dst)");
@@ -390,7 +424,11 @@ const char *thvm_cuda_last_error(void) {
 }
 void thvm_cuda_clear_error(void) { g.last_error.clear(); }
 void *thvm_cuda_stream(void) { return (void *)g.stream; }
-void thvm_cuda_sync(void) { if (g.ready && !g.cap) THC_CUDA_OK(cudaStreamSynchronize(g.stream)); }
+void thvm_cuda_sync(void) {
+    if (!g.ready || g.cap) return;
+    THC_CUDA_OK(cudaStreamSynchronize(g.stream));
+    THC_CUDA_OK(cudaStreamSynchronize(g.copy_stream));
+}
 void *thvm_cuda_buf_ptr(uint32_t id) {
     if (!(g.ready && id && id < THC_MAX_BUFS && g.bufs[id].live)) return nullptr;
     Buf &b = buf_checked(id, "buf_ptr");    // attaches device memory if the buffer was host-only

@@ -21,6 +21,7 @@ struct Buf {
     uint8_t *shadow   = nullptr;   // host copy of a small host-written buffer
     bool     shadow_valid = false; // false once a kernel or copy wrote the buffer
     bool     zero_pending = false; // fresh device memory whose zero-fill has not been issued yet
+    bool     copy_pending = false; // an asynchronous read-back of this buffer may still be in flight on the copy stream
     bool     plain_alloc = false;  // ptr came from cudaMalloc (attached while a step was being captured), not from the stream-ordered pool
 };
 
@@ -31,6 +32,8 @@ struct State {
     int          device = 0;
     int          sm_count = 148;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;   // device->host copies of buf_read_async, so they overlap uploads and kernels on `stream`
+    cudaEvent_t  copy_after = nullptr, copy_done = nullptr;
     Buf          bufs[THC_MAX_BUFS];
     uint32_t     count = 1;          // next id; 0 is the null buffer
     uint32_t     persistent = 0;     // ids <= this survive decref
@@ -81,6 +84,8 @@ Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written);
 Buf &buf_live(uint32_t id, const char *who);
 // scratch of at least `bytes` (stream-ordered reuse: all users run on g.stream)
 void *scratch_reserve(uint64_t bytes);
+// before `b` is overwritten or freed on the main stream: wait for a read-back of it that may still be running
+void fence_copy(Buf &b);
 // mark a buffer as written by the device
 inline void mark_device_written(uint32_t id) { g.bufs[id].shadow_valid = false; }
 // grid size helper: enough CTAs to fill the machine `waves` times over
