@@ -216,6 +216,9 @@ const char *thvm_cuda_last_plan(void);
 /* Plan selection override for tests: 0 = automatic, 1 = always the generic
  * descriptor-driven kernel. */
 void     thvm_cuda_set_force_generic(int on);
+/* Number of plans in the signature-keyed cache (a dispatch refused while a step is being
+ * captured leaves none behind). */
+uint64_t thvm_cuda_plan_count(void);
 
 /* Signature of a dispatch, the same FNV-style mix the reference computes as
  * `normalized_sig` (src/tinyhvm.h:828-856); the plan cache is keyed by it. */
@@ -296,7 +299,10 @@ int      thvm_cuda_argmax_rows(uint32_t out_u32, uint32_t x, uint32_t rows, uint
  *   - All calls on a device share the array and it keeps the previous call's
  *     contents; every slot is rewritten before it is read, so no clearing is
  *     needed, but two calls whose kernels overlap on the GPU (different
- *     streams) race on it — serialise them. */
+ *     streams) race on it — serialise them.
+ *   - The first call on a device is not safe against another host thread making
+ *     its own first call on that device at the same moment: make one call per
+ *     device from one thread before sharing the entry point between threads. */
 int      thvm_cuda_channel_sums_noalloc(const float *x, float *out, uint32_t B, uint32_t C, uint32_t HW, void *stream);
 
 #ifdef __cplusplus

@@ -95,7 +95,9 @@ class Reference:
         so = ORACLE_DIR / "_ref" / "libthvm_cpu_ref.so"
         if not so.exists():
             try:
-                subprocess.run(["make", "-C", str(ORACLE_DIR), "ref"], check=True, capture_output=True)
+                import os
+                ref = os.environ.get("THVM_REFERENCE") or str(ROOT.parent / "reference")
+                subprocess.run(["make", "-C", str(ORACLE_DIR), "ref", f"REF={ref}"], check=True, capture_output=True)
             except Exception:
                 return None
         return cls(so) if so.exists() else None

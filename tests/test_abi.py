@@ -55,3 +55,15 @@ def test_view_algebra_canonical_forms():
     assert abi.view_dims(w) == [1, 1, 2, 2, 2, 2] and abi.view_strides(w) == [0, 0, 3, 1, 3, 1]
     s = abi.view_shrink(abi.view_contiguous([4, 5]), [1, 2], [3, 5])
     assert abi.view_dims(s) == [2, 3] and s.offset == 7
+
+
+def test_dp_allreduce_refuses_bad_buffers_before_any_collective():
+    """An argument error must come back before a collective is opened (a rank that issued a shorter group than its
+    peers would leave them waiting): ids that are not live are refused with return code 1 on the spot."""
+    lib = tinyhvm_b200.load()
+    ids = (C.c_uint32 * 2)(123, 0)
+    counts = (C.c_uint64 * 2)(16, 16)
+    lib.thvm_cuda_clear_error()
+    assert lib.thvm_cuda_dp_allreduce_sum(ids, counts, 2) == 1
+    assert b"not live" in lib.thvm_cuda_last_error()
+    lib.thvm_cuda_clear_error()

@@ -132,6 +132,15 @@ def test_pool_contract(cuda):
     cuda.reset(a - 1)
     assert cuda.alloc(16) == a                             # counter rewound
     cuda.reset(a - 1)
+    # a kernel writes a small buffer, the host then overwrites its first element only: the rest comes from the device
+    src = cuda.upload(np.arange(10, dtype=np.float32))
+    small = cuda.alloc(40)
+    lib.thvm_cuda_buf_copy(small, src, 40)                 # both host-only: stays a host copy
+    vd = abi.view_contiguous([10])
+    cuda.dispatch_ids(small, [src, src], abi.Dispatch([abi.Leaf(None, vd), abi.Leaf(None, vd)], [(abi.ADD, 0, 1)], [10]))
+    cuda.write(small, np.array([100.0], dtype=np.float32))
+    assert cuda.read(small, np.float32, 10).tolist() == [100.0] + [2.0 * i for i in range(1, 10)]
+    cuda.reset(a - 1)
     # reads past the end of a buffer return zeros
     e = cuda.upload(np.ones(4, dtype=np.float32))
     assert cuda.read(e, np.float32, 8).tolist() == [1, 1, 1, 1, 0, 0, 0, 0]

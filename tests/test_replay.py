@@ -239,3 +239,72 @@ def test_capture_refuses_a_step_that_leaks_a_buffer(cuda):
     a = cuda.upload(np.arange(1024, dtype=np.float32))
     assert np.array_equal(cuda.read(a, np.float32, 1024), np.arange(1024, dtype=np.float32))    # the backend is still usable
     cuda.reset(0)
+
+
+@pytest.mark.gpu
+def test_capture_refuses_a_dispatch_it_has_not_seen_and_caches_no_plan(cuda):
+    """A dispatch whose plan does not exist yet cannot be built while the stream records (its tables would live in
+    memory the recorded graph owns).  The capture is refused before anything is allocated, the plan cache is left as
+    it was, and the same dispatch then runs eagerly with the right result."""
+    import cases
+    from tinyhvm_b200 import abi
+    cuda.reset(0)
+    rng = np.random.default_rng(11)
+    # shapes no other test uses, so the plans cannot exist yet: a tracker leaf (device tables), a contraction
+    # (offset tables) and a non-f32 output (descriptor-driven kernel)
+    fresh = [cases.tracker_case(987654), cases.mm_case(rng, 77, 131, 59)]
+    for d in fresh:
+        ids = [cuda.upload(l.data) for l in d.leaves]
+        out = cuda.alloc(d.out_numel * 4)
+        cuda.sync()
+        plans = cuda.lib.thvm_cuda_plan_count()
+        assert cuda.lib.thvm_cuda_capture_begin() == 0
+        cuda.dispatch_ids(out, ids, d)
+        assert cuda.lib.thvm_cuda_capture_end() == 0
+        assert "inside the captured step" in cuda.last_error()
+        cuda.clear_error()
+        assert cuda.lib.thvm_cuda_plan_count() == plans, "a plan built inside the refused capture stayed in the cache"
+        cuda.dispatch_ids(out, ids, d)                      # eager: builds the plan now
+        got = cuda.read(out, np.float32, d.out_numel)
+        want = cases_oracle().run(d)
+        assert np.allclose(got, want, rtol=1e-4, atol=1e-5), d.name
+        assert cuda.lib.thvm_cuda_plan_count() == plans + 1
+        cuda.reset(0)
+    assert cuda.last_error() == ""
+
+
+def cases_oracle():
+    import checkers
+    return checkers.Oracle()
+
+
+@pytest.mark.gpu
+def test_refused_capture_leaves_older_buffers_as_they_were(cuda):
+    """Buffers that existed before a refused capture keep their contents: a small host-written constant that the
+    captured step was the first to touch on the device still feeds later kernels correctly, a fresh buffer still reads
+    as zero, and a host write made inside the refused step is gone."""
+    from tinyhvm_b200 import abi
+    from tinyhvm_b200.abi import ADD, Dispatch, Leaf
+    cuda.reset(0)
+    n = 4096
+    x = np.arange(n, dtype=np.float32)
+    d = Dispatch([Leaf(x, abi.view_contiguous([n])), Leaf(np.array([2.5], np.float32), abi.view_contiguous([1]))], [(ADD, 0, 1)], [n])
+    bx, bs = cuda.upload(x), cuda.upload(np.array([2.5], np.float32))   # bs: host shadow only so far
+    fresh = cuda.alloc(n * 4)                                            # owes its zero-fill
+    out = cuda.alloc(n * 4)
+    cuda.dispatch_ids(out, [bx, cuda.upload(np.array([1.0], np.float32))], d)   # plan exists now; its scalar buffer is a third one
+    cuda.sync()
+    assert cuda.lib.thvm_cuda_capture_begin() == 0
+    cuda.dispatch_ids(out, [bx, bs], d)                                  # first device use of bs happens inside the capture
+    cuda.dispatch_ids(fresh, [bx, bs], d)                                # would overwrite the fresh buffer
+    cuda.write(bs, np.array([7.0], np.float32))                          # host write inside the step
+    leaked = cuda.alloc(1 << 16)                                         # makes the capture fail
+    assert cuda.lib.thvm_cuda_capture_end() == 0
+    cuda.clear_error()
+    assert cuda.read(bs, np.float32, 1)[0] == 2.5
+    assert not cuda.read(fresh, np.float32, n).any()
+    out2 = cuda.alloc(n * 4)
+    cuda.dispatch_ids(out2, [bx, bs], d)
+    assert np.array_equal(cuda.read(out2, np.float32, n), x + np.float32(2.5))
+    cuda.reset(0)
+    assert cuda.last_error() == ""

@@ -65,6 +65,7 @@ SYMBOLS = {
     "thvm_cuda_launch_count": (_u64, []),
     "thvm_cuda_last_plan": (C.c_char_p, []),
     "thvm_cuda_set_force_generic": (None, [C.c_int]),
+    "thvm_cuda_plan_count": (_u64, []),
     "thvm_cuda_dp_unique_id": (C.c_int, [_vp]),
     "thvm_cuda_dp_init": (C.c_int, [C.c_int, C.c_int, _vp]),
     "thvm_cuda_dp_world": (C.c_int, []),

@@ -35,6 +35,9 @@ struct Capture {
     std::vector<Result> results;
     uint64_t launches = 0, launches_at_begin = 0;
     uint32_t first_id = 0;
+    // host-side state of every buffer that existed when the capture began, put back if the capture is refused
+    struct Snap { uint32_t id; void *ptr; uint32_t refcount; bool shadow_valid, zero_pending, plain_alloc; uint8_t shadow[256]; };
+    std::vector<Snap> snaps;
     bool failed = false;
     std::string why;
 };
@@ -133,6 +136,13 @@ int thvm_cuda_capture_begin(void) {
     Capture *c = new Capture();
     c->first_id = g.count;
     c->launches_at_begin = g.launches;
+    for (uint32_t i = 1; i < c->first_id; i++) {
+        const Buf &b = g.bufs[i];
+        if (!b.live) continue;
+        Capture::Snap sn{i, b.ptr, b.refcount, b.shadow_valid, b.zero_pending, b.plain_alloc, {0}};
+        if (b.shadow) memcpy(sn.shadow, b.shadow, sizeof sn.shadow);
+        c->snaps.push_back(sn);
+    }
     cudaError_t e = cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed);
     if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_begin: %s", cudaGetErrorString(e)); delete c; return 1; }
     g.cap = c;
@@ -158,10 +168,22 @@ int thvm_cuda_capture_end(void) {
     g.cap = nullptr;
     // buffers the step left behind point into memory of a graph that will never run: forget them
     // (no free call: the addresses belong to the graph) and rewind the ids, as if the step had not happened
+    // The older buffers go back to the host-side state they had when the capture began: shadows, reference counts and
+    // "host copy is current" flags changed by the step's writes and launches, none of which ran.  Device memory that
+    // was attached to a host-only buffer meanwhile is released again (its upload came from the shadow being restored).
     auto forget_leftovers = [&]() {
         for (uint32_t i = c->first_id; i < THC_MAX_BUFS; i++)
             if (g.bufs[i].live) { free(g.bufs[i].shadow); g.bufs[i] = Buf(); }
         if (g.count > c->first_id) g.count = c->first_id;
+        for (const Capture::Snap &sn : c->snaps) {
+            Buf &b = g.bufs[sn.id];
+            if (!b.live) continue;                     // the step freed it (already reported as the reason for the refusal)
+            if (b.ptr && !sn.ptr) { cudaFree(b.ptr); b.ptr = nullptr; b.plain_alloc = false; }
+            b.refcount = sn.refcount; b.shadow_valid = sn.shadow_valid;
+            if (sn.ptr) b.zero_pending = b.zero_pending && sn.zero_pending;   // a zero-fill done meanwhile really ran
+            else b.zero_pending = false;
+            if (b.shadow) memcpy(b.shadow, sn.shadow, sizeof sn.shadow);
+        }
     };
     if (e != cudaSuccess || !c->graph) { cudaGetLastError(); set_error("capture_end: %s", cudaGetErrorString(e)); forget_leftovers(); destroy(c); return 0; }
     if (c->failed) { set_error("capture_end: %s", c->why.c_str()); forget_leftovers(); destroy(c); return 0; }

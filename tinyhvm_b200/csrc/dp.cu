@@ -14,6 +14,7 @@
 // NCCL is opened with dlopen at dp_init, so a single-GPU user needs no NCCL.
 #include <dlfcn.h>
 #include <string.h>
+#include <vector>
 #include "state.h"
 
 namespace thc {
@@ -99,15 +100,24 @@ int thvm_cuda_dp_rank(void) { return nccl.rank; }
 // in-place sum over all ranks of the first `n` floats of each buffer; one NCCL group
 // (one bucket) per call, stream-ordered after the kernels that wrote the buffers
 int thvm_cuda_dp_allreduce_sum(const uint32_t *buf_ids, const uint64_t *counts, uint32_t n_bufs) {
+    // Validate and resolve everything before the group opens: a rank that left the group early would leave the
+    // other ranks' collectives without a peer.
+    if (n_bufs > 4096) { set_error("dp_allreduce: %u buffers in one call", n_bufs); return 1; }
+    std::vector<void *> ptrs(n_bufs);
+    for (uint32_t i = 0; i < n_bufs; i++) {
+        const uint32_t id = buf_ids[i];
+        if (id == 0 || id >= THC_MAX_BUFS || !g.bufs[id].live) { set_error("dp_allreduce: buffer id %u is not live", id); return 1; }
+        if (counts[i] * 4 > g.bufs[id].bytes) { set_error("dp_allreduce: %llu floats exceed buffer %u", (unsigned long long)counts[i], id); return 1; }
+    }
     if (nccl.world == 1) return 0;
     if (!nccl.comm) { set_error("dp_allreduce: dp_init has not run"); return 1; }
-    bool ok = nccl_ok(nccl.GroupStart(), "ncclGroupStart");
-    for (uint32_t i = 0; i < n_bufs && ok; i++) {
-        Buf &b = buf_checked(buf_ids[i], "dp_allreduce");
-        if (counts[i] * 4 > b.bytes) { set_error("dp_allreduce: %llu floats exceed buffer %u", (unsigned long long)counts[i], buf_ids[i]); ok = false; break; }
+    for (uint32_t i = 0; i < n_bufs; i++) {
+        ptrs[i] = buf_checked(buf_ids[i], "dp_allreduce").ptr;
         mark_device_written(buf_ids[i]);
-        ok = nccl_ok(nccl.AllReduce(b.ptr, b.ptr, (size_t)counts[i], ncclFloat32, ncclSum, nccl.comm, g.stream), "ncclAllReduce");
     }
+    bool ok = nccl_ok(nccl.GroupStart(), "ncclGroupStart");
+    for (uint32_t i = 0; i < n_bufs && ok; i++)
+        ok = nccl_ok(nccl.AllReduce(ptrs[i], ptrs[i], (size_t)counts[i], ncclFloat32, ncclSum, nccl.comm, g.stream), "ncclAllReduce");
     ok = nccl_ok(nccl.GroupEnd(), "ncclGroupEnd") && ok;
     return ok ? 0 : 1;
 }

@@ -754,8 +754,7 @@ static void launch_with(const FastDesc &F, const FDesc &D, float *out) {
     }
     if (F.rows) {
         const unsigned long long R = D.numel / D.dims[D.rank - 1];
-        static const unsigned rows_cta_min = getenv("THVM_ROWS_CTA_MIN") ? (unsigned)atoi(getenv("THVM_ROWS_CTA_MIN")) : 2048u;
-        const bool cta = D.dims[D.rank - 1] / 4 >= rows_cta_min;
+        const bool cta = D.dims[D.rank - 1] / 4 >= 2048u;      // a CTA per row once a row gives every thread 8 vectors
         const unsigned grid = cta ? (unsigned)(R < 0x7FFFFFFFull ? R : 0x7FFFFFFFull) : grid_for(R, 8, 8);
         if (F.strategy == 0) {
             if (cta) k_rowsx<EV, 256, false><<<grid, 256, 0, g.stream>>>(D, out);

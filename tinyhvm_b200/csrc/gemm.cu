@@ -45,7 +45,6 @@ constexpr int UNITS = 1024 / NPROD;                 // (row, 16-byte chunk) unit
 constexpr int GEMM_THREADS = NPROD + 32;            // + 1 MMA warp
 constexpr int MMA_WARP = PROD_WARPS;
 constexpr int TMEM_COLS = 128;
-constexpr int PREFETCH_AHEAD = 8;                   // k-blocks between an L2 prefetch and its cp.async
 constexpr int LOOKAHEAD = 2;                        // k-blocks of cp.async in flight ahead of the split pass
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 enum : int { ERR_GEMM_TIMEOUT = 8 };
@@ -184,19 +183,6 @@ __device__ __forceinline__ void issue_tile(const UnitSet &U, const float *P, con
         }
     }
 }
-// pull the 128-byte lines a later k-block will need into L2 (one request per line:
-// only the thread owning chunk 0 of a row asks, and only for 16-byte-vector operands,
-// whose rows are contiguous in k)
-__device__ __forceinline__ void prefetch_tile(const UnitSet &U, long long klin, const int32_t *__restrict__ ktab,
-                                              uint32_t k0, uint32_t K, uint32_t kvec) {
-    if (!kvec || k0 >= K) return;
-#pragma unroll
-    for (int i = 0; i < UNITS; i++)
-        if (U.kcol[i] == 0 && ((U.live >> i) & 1u)) {
-            const float *p = U.rowptr[i] + (klin ? (long long)k0 * klin : (long long)ktab[k0]);
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-        }
-}
 // low-part pass over this thread's own units: lo = x - trunc_tf32(x).  The raw f32
 // tile doubles as the high part: the tf32 MMA reads only the upper 19 bits.
 __device__ __forceinline__ void split_tile(const UnitSet &U, uint32_t raw_tile, uint32_t lo_tile) {
@@ -217,7 +203,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
     // tile order: bands of 8 row-tiles, column-tiles fastest inside a band, so the CTAs
     // that run together share a few A and B panels that stay in L2
     const uint32_t tm = (G.M + BM - 1) / BM, tn = (G.N + BN - 1) / BN;
-    const uint32_t BH = G.band ? G.band : 1u;
+    const uint32_t BH = 8u;                                          // band height in row tiles
     const uint32_t band = BH * tn, b0 = (blockIdx.x / band) * BH;
     const uint32_t bh = tm - b0 < BH ? tm - b0 : BH, within = blockIdx.x % band;
     const uint32_t m0 = (b0 + within % bh) * BM, n0 = (within / bh) * BN;
@@ -272,7 +258,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
         };
         // prologue: LOOKAHEAD k-blocks in flight (one commit group per k-block, empty groups keep the count uniform)
         for (uint32_t kb = 0; kb < (uint32_t)LOOKAHEAD; kb++) {
-            if (kb < nkb && G.debug_mode != 1 && G.debug_mode != 3) issue(kb);
+            if (kb < nkb) issue(kb);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         for (uint32_t kb = 0; kb < nkb && ok; kb++) {
@@ -285,10 +271,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
                 if (!ok) break;
             }
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, lo = tiles_s + LO_BASE + (kb % LO_STAGES) * STAGE_BYTES;
-            if (G.debug_mode != 1 && G.debug_mode != 4) {
-                split_tile(UA, st, lo);
-                split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
-            }
+            split_tile(UA, st, lo);
+            split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");              // generic-proxy writes -> visible to the MMA
             mbar_arrive(smem_u32(&S.full[kb % STAGES]));
             // refill the raw stage whose MMAs (k-block kb - 1) finish next: three k-blocks of copies stay in flight
@@ -296,7 +280,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
             if (nxt < nkb) {
                 const uint32_t use = nxt / STAGES;                       // stage (nxt % STAGES) was last read by k-block nxt - STAGES
                 if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[nxt % STAGES]), (use - 1) & 1u, abort_flag);
-                if (ok && G.debug_mode != 1 && G.debug_mode != 3) issue(nxt);
+                if (ok) issue(nxt);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -354,7 +338,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) k_gemm_3xtf32(const __grid_co
                 const uint64_t a_hi = umma_desc(st), b_hi = umma_desc(st + TILE_BYTES);
                 const uint64_t a_lo = umma_desc(lo), b_lo = umma_desc(lo + TILE_BYTES);
 #pragma unroll
-                for (uint32_t ks = 0; ks < (G.debug_mode >= 2 ? 0u : (uint32_t)(BK / 8)); ks++) {
+                for (uint32_t ks = 0; ks < (uint32_t)(BK / 8); ks++) {
                     const uint64_t adv = (uint64_t)(ks * 2u);           // 8 tf32 = 32 bytes, in 16-byte units
                     umma_tf32(tmem, a_lo + adv, b_hi + adv, UMMA_IDESC, (kb | ks) ? 1u : 0u);
                     umma_tf32(tmem, a_hi + adv, b_lo + adv, UMMA_IDESC, 1u);
@@ -496,33 +480,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) k_g
         auto issue = [&](uint32_t kb) {
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, k0 = (kb_lo + kb) * BK;
             issue_tile(UA, G.A, G.ka, G.a_klin, k0, G.K, G.a_kvec, st);
-            if (G.debug_mode != 6) issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + TILE_BYTES);
+            issue_tile(UB, G.B, G.kb, G.b_klin, k0, G.K, G.b_kvec, st + TILE_BYTES);
         };
-        const uint32_t dbg = G.debug_mode;                               // timing experiments: 1 MMAs only, 2 no MMAs, 3 no copies, 4 no low-part pass
         for (uint32_t kb = 0; kb < (uint32_t)LOOKAHEAD; kb++) {
-            if (kb < nkb && dbg != 1 && dbg != 3) issue(kb);
+            if (kb < nkb) issue(kb);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
         for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-            if (dbg != 5) asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
+            asm volatile("cp.async.wait_group %0;" ::"n"(LOOKAHEAD - 1) : "memory");
             if (kb >= (uint32_t)LO_STAGES) {
                 const uint32_t prev = kb - LO_STAGES;
                 ok = mbar_wait(smem_u32(&S.empty[prev % STAGES]), (prev / STAGES) & 1u, abort_flag);
                 if (!ok) break;
             }
             const uint32_t st = tiles_s + (kb % STAGES) * STAGE_BYTES, lo = tiles_s + LO_BASE + (kb % LO_STAGES) * STAGE_BYTES;
-            if (dbg != 1 && dbg != 4) {
-                split_tile(UA, st, lo);
-                split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
-            }
-            if (dbg != 7) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            split_tile(UA, st, lo);
+            split_tile(UB, st + TILE_BYTES, lo + TILE_BYTES);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&S.full[kb % STAGES]), 0));   // one arrival per warp, on the first CTA's barrier
             const uint32_t nxt = kb + LOOKAHEAD;
             if (nxt < nkb) {
                 const uint32_t use = nxt / STAGES;
                 if (use >= 1) ok = mbar_wait(smem_u32(&S.empty[nxt % STAGES]), (use - 1) & 1u, abort_flag);
-                if (ok && dbg != 1 && dbg != 3) issue(nxt);
+                if (ok) issue(nxt);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -582,7 +563,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) k_g
                 const uint64_t a_hi = umma_desc(st), b_hi = umma_desc(st + TILE_BYTES);
                 const uint64_t a_lo = umma_desc(lo), b_lo = umma_desc(lo + TILE_BYTES);
 #pragma unroll
-                for (uint32_t ks = 0; ks < (G.debug_mode == 2 ? 0u : (uint32_t)(BK / 8)); ks++) {
+                for (uint32_t ks = 0; ks < (uint32_t)(BK / 8); ks++) {
                     const uint64_t adv = (uint64_t)(ks * 2u);
                     umma2_tf32(tmem, a_lo + adv, b_hi + adv, idesc, (kb | ks) ? 1u : 0u);
                     umma2_tf32(tmem, a_hi + adv, b_lo + adv, idesc, 1u);

@@ -31,8 +31,6 @@ struct GemmDesc {
     uint32_t b_kfast, b_kvec;
     long long a_klin, b_klin;          // non-zero: the operand's k offset is k * klin (one reduced dim, no table lookup)
     uint32_t c_nvec;                   // C: n is contiguous and 16-byte aligned per row
-    uint32_t debug_mode;               // timing experiments only: 1 = MMAs without operand traffic, 2 = operand traffic without MMAs
-    uint32_t band, prefetch;           // tile-order band height (row tiles); L2 prefetch on/off
     uint32_t kb_chunk;                 // k-blocks (of 32) per split; gridDim.z splits share one output tile
     uint32_t n_half;                   // CTA-pair kernel: B rows (output columns) each CTA of a pair loads: 128, 64 or 32
     float *partial;                    // split-K: dense [split][M][N] partial sums (library scratch), else null

@@ -148,19 +148,25 @@ static bool build_desc(Plan *p, const thc_view_t **views, const thc_tracker_t *c
     p->n_trackers = (uint32_t)trackers.size();
     if (!trackers.empty()) {
         uint64_t bytes = trackers.size() * sizeof(DTracker);
-        THC_CUDA_OK(cudaMallocAsync((void **)&p->dev_trackers, bytes, g.stream));
+        THC_CUDA_OK(cudaMallocAsync((void **)&p->dev_trackers, bytes, g.stream));   // never inside a capture: the caller refuses first
         THC_CUDA_OK(cudaMemcpyAsync(p->dev_trackers, trackers.data(), bytes, cudaMemcpyHostToDevice, g.stream));
-        if (capturing()) capture_fail("a plan was built inside the captured step: run the step once before capturing it");
-        else THC_CUDA_OK(cudaStreamSynchronize(g.stream));   // `trackers` dies with this scope
+        THC_CUDA_OK(cudaStreamSynchronize(g.stream));        // `trackers` dies with this scope
         D.trackers = p->dev_trackers;
     }
     return true;
 }
 
-static void ensure_dev_desc(Plan *p) {
-    if (p->dev_desc) return;
+// The device copy of the descriptor, made the first time the generic kernel runs the plan.  Memory allocated while a
+// step is being recorded would belong to the recorded graph, so inside a capture this refuses instead (false).
+static bool ensure_dev_desc(Plan *p) {
+    if (p->dev_desc) return true;
+    if (capturing()) {
+        capture_fail("a dispatch met the descriptor-driven kernel for the first time inside the captured step: run the step once before capturing it");
+        return false;
+    }
     THC_CUDA_OK(cudaMallocAsync((void **)&p->dev_desc, sizeof(GenDesc), g.stream));
     upload_small(p->dev_desc, &p->host, sizeof(GenDesc));
+    return true;
 }
 
 void launch_generic(const GenDesc &H, const GenDesc *dev_desc, const GenArgs &args);   // generic.cu
@@ -170,6 +176,9 @@ void launch_generic(const GenDesc &H, const GenDesc *dev_desc, const GenArgs &ar
 using namespace thc;
 
 extern "C" {
+
+// number of cached plans (tests: a dispatch refused inside a capture must leave none behind)
+uint64_t thvm_cuda_plan_count(void) { return cache ? (uint64_t)cache->size() : 0; }
 
 void plan_cache_clear(void) {
     if (!cache) return;
@@ -205,6 +214,9 @@ void thvm_cuda_dispatch_kernel_rs(uint32_t out_buf, uint32_t *leaf_bufs, const t
     auto it = cache->find(key);
     if (it != cache->end()) p = it->second;
     else {
+        // Building a plan allocates device tables and waits for their upload; neither can happen while the stream is
+        // recording.  The step is refused before anything is allocated, and nothing enters the cache.
+        if (capturing()) { capture_fail("a plan was built inside the captured step: run the step once before capturing it"); return; }
         p = new Plan();
         if (!build_desc(p, leaf_views, leaf_sts, n_leaves, ops, n_ops, full_shape, red, leaf_dtypes, out_dtype)) {
             plan_free(p);
@@ -234,7 +246,7 @@ void thvm_cuda_dispatch_kernel_rs(uint32_t out_buf, uint32_t *leaf_bufs, const t
         return;
     }
     if (p->kind != PLAN_GENERIC && launch_fast(p, args)) return;
-    ensure_dev_desc(p);
+    if (!ensure_dev_desc(p)) return;
     launch_generic(p->host, p->dev_desc, args);
 }
 

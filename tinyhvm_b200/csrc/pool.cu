@@ -31,7 +31,6 @@ State g;
 
 static const uint64_t RING_BYTES   = 16ull << 20;   // two 8 MiB halves
 static const uint64_t RING_MAX_MSG = 1ull << 20;    // larger writes go direct
-static const uint64_t SHADOW_MAX   = 256;
 
 void set_error(const char *fmt, ...) {
     char tmp[512];
@@ -55,19 +54,40 @@ Buf &buf_live(uint32_t id, const char *who) {
 
 static uint8_t *ring_take(uint64_t bytes);
 void fence_copy(Buf &b);
+static const uint64_t SHADOW_MAX   = 256;
+
+// A buffer that existed before a capture began outlives the recorded step, so what it needs to become usable — device
+// memory, the upload of its host shadow, the zero-fill a fresh buffer owes — must really happen, not merely be recorded:
+// it is done at once on the copy stream (which is not recording) and waited for.  The recorded step then finds the
+// buffer in the state an eager step would, whether or not the capture ends up being used.
+static void settle_outside_capture(Buf &b, bool attach) {
+    const uint64_t sz = ((b.bytes + 15) & ~15ull) ? ((b.bytes + 15) & ~15ull) : 16;
+    if (attach) {
+        THC_CUDA_OK(cudaMalloc(&b.ptr, sz));
+        b.plain_alloc = true;
+        if (b.shadow && b.shadow_valid && b.bytes) {
+            uint8_t tmp[SHADOW_MAX + 16] = {0};
+            memcpy(tmp, b.shadow, b.bytes);
+            THC_CUDA_OK(cudaMemcpyAsync(b.ptr, tmp, sz, cudaMemcpyHostToDevice, g.copy_stream));
+        } else {
+            THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.copy_stream));
+        }
+    } else {
+        THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.copy_stream));
+    }
+    THC_CUDA_OK(cudaStreamSynchronize(g.copy_stream));
+    b.zero_pending = false;
+}
 
 Buf &buf_checked(uint32_t id, const char *who) {
     Buf &b = buf_live(id, who);
     fence_copy(b);                                  // whatever comes next on the main stream stays behind a running read-back of b
+    const bool outlives_capture = g.cap && id < capture_first_id();
     if (!b.ptr) {                                   // host-only so far: attach device memory now
+        if (outlives_capture) { settle_outside_capture(b, true); return b; }
         uint64_t sz = (b.bytes + 15) & ~15ull;
         if (sz == 0) sz = 16;
-        if (g.cap && id < capture_first_id()) {     // outlives the captured step: must not become memory the graph owns
-            THC_CUDA_OK(cudaMalloc(&b.ptr, sz));
-            b.plain_alloc = true;
-        } else {
-            THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
-        }
+        THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
         if (b.shadow && b.shadow_valid && b.bytes) {
             uint8_t *stage = ring_take(sz);
             memset(stage, 0, sz);
@@ -78,6 +98,7 @@ Buf &buf_checked(uint32_t id, const char *who) {
         }
     }
     if (b.zero_pending) {
+        if (outlives_capture) { settle_outside_capture(b, false); return b; }
         THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
         b.zero_pending = false;
     }
@@ -93,7 +114,8 @@ void fence_copy(Buf &b) {
 Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written) {
     Buf &b = buf_live(id, who);
     fence_copy(b);
-    if (b.ptr && b.zero_pending && bytes_written >= b.bytes) b.zero_pending = false;
+    // (not for a buffer that outlives a running capture: the overwrite is only being recorded)
+    if (b.ptr && b.zero_pending && bytes_written >= b.bytes && !(g.cap && id < capture_first_id())) b.zero_pending = false;
     return buf_checked(id, who);
 }
 
@@ -321,12 +343,19 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
         bytes = b.bytes;
     }
     if (bytes == 0) return;
-    if (b.shadow) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
+    if (b.shadow) {
+        // the shadow speaks for the whole buffer only if it did before, or if this write covers all of it
+        // (after a kernel wrote the buffer, a partial host write leaves the rest on the device only)
+        if (b.shadow_valid || bytes >= b.bytes) { memcpy(b.shadow, data, bytes); b.shadow_valid = true; }
+    }
     if (!b.ptr) return;                            // host-only buffer: uploaded if and when the device needs it
     fence_copy(b);
     if (b.zero_pending) {
-        if (bytes < b.bytes) THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
-        b.zero_pending = false;
+        if (g.cap && id < capture_first_id()) settle_outside_capture(b, false);
+        else {
+            if (bytes < b.bytes) THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, (b.bytes + 15) & ~15ull, g.stream));
+            b.zero_pending = false;
+        }
     }
     if (bytes <= RING_MAX_MSG) {
         uint8_t *stage = ring_take(bytes);
@@ -392,7 +421,7 @@ void thvm_cuda_buf_copy(uint32_t dst_buf, uint32_t src_buf, uint64_t nbytes) {
     }
     if (n == 0) return;
     THC_CUDA_OK(cudaMemcpyAsync(d.ptr, s.ptr, n, cudaMemcpyDeviceToDevice, g.stream));
-    if (d.shadow && s.shadow && s.shadow_valid) { memcpy(d.shadow, s.shadow, n); d.shadow_valid = true; }
+    if (d.shadow && s.shadow && s.shadow_valid && (d.shadow_valid || n >= d.bytes)) { memcpy(d.shadow, s.shadow, n); d.shadow_valid = true; }
     else d.shadow_valid = false;
 }
 

@@ -30,6 +30,7 @@ struct KArgs {
     void *out; uint64_t out_cap;
     const void *leaf[THC_MAX_LEAVES]; uint64_t cap[THC_MAX_LEAVES];
     uint64_t total; int *status;
+    uint64_t fuel;                       // op executions one gid may take: the host's count for this program, doubled
 };
 
 __device__ __forceinline__ bool k_is_float(uint32_t type) {
@@ -52,8 +53,9 @@ __global__ void __launch_bounds__(128) k_uop(const KProg *__restrict__ P, const 
          gid += (uint64_t)gridDim.x * blockDim.x) {
         for (uint32_t i = 0; i < n; i++) reg[i] = 0u;
         uint32_t pc = 0;
-        uint64_t fuel = 1ull << 40;       // a malformed program cannot spin forever
-        while (pc < n && fuel--) {
+        uint64_t fuel = A.fuel;           // the host counted what a well-formed run needs; running out is reported, not spun on
+        while (pc < n) {
+            if (fuel-- == 0) { atomicOr(A.status, ERR_BAD_PROGRAM); break; }
             const thc_kop_t op = P->ops[pc];
             switch (op.type) {
                 case THC_KOP_GID:      reg[pc] = (uint32_t)gid; break;
@@ -345,17 +347,32 @@ void thvm_cuda_dispatch_uop_kernel(uint32_t out_buf, const uint32_t *leaf_bufs, 
     memset(&hp, 0, sizeof hp);
     hp.n_ops = kernel->n_ops; hp.n_leaves = n_leaves; hp.out_dtype = kernel->out_dtype;
     for (uint32_t i = 0; i < n_leaves; i++) hp.leaf_dtypes[i] = kernel->leaf_dtypes[i];
+    // Loop structure, and the number of op executions one gid performs: every op runs once per trip of the loops
+    // around it.  A program whose nested trip counts multiply out beyond UOP_MAX_STEPS per gid is refused here
+    // instead of being left to occupy the GPU (the largest reduce range a reference kernel carries is 2^32).
+    constexpr double UOP_MAX_STEPS = 34359738368.0;   // 2^35
     uint32_t stack[THC_KOP_MAX], sp = 0;
+    double trips = 1.0, steps = 0.0;
     for (uint32_t i = 0; i < kernel->n_ops; i++) {
         hp.ops[i] = kernel->ops[i];
-        if (kernel->ops[i].type == THC_KOP_RANGE) stack[sp++] = i;
-        else if (kernel->ops[i].type == THC_KOP_ENDRANGE) {
+        if (kernel->ops[i].type == THC_KOP_RANGE) {
+            steps += trips;
+            stack[sp++] = i;
+            trips *= (double)(kernel->ops[i].imm.u ? kernel->ops[i].imm.u : 1u);
+            continue;
+        }
+        if (kernel->ops[i].type == THC_KOP_ENDRANGE) {
             if (sp == 0) { set_error("uop kernel: ENDRANGE without RANGE at %u", i); return; }
             uint32_t s = stack[--sp];
             hp.range_end[s] = i; hp.range_start[i] = s;
+            steps += trips;
+            trips /= (double)(kernel->ops[s].imm.u ? kernel->ops[s].imm.u : 1u);
+            continue;
         }
+        steps += trips;
     }
     if (sp != 0) { set_error("uop kernel: unclosed RANGE"); return; }
+    if (steps > UOP_MAX_STEPS) { set_error("uop kernel: %.3g op executions per output exceed the limit of %.3g", steps, UOP_MAX_STEPS); return; }
 
     Buf &ob = buf_checked(out_buf, "dispatch_uop(out)");
     KArgs a; memset(&a, 0, sizeof a);
@@ -367,6 +384,7 @@ void thvm_cuda_dispatch_uop_kernel(uint32_t out_buf, const uint32_t *leaf_bufs, 
     a.total = kernel->local_size > 0 ? kernel->grid[0]
                                      : (uint64_t)kernel->grid[0] * kernel->grid[1] * kernel->grid[2];
     a.status = g.dev_status;
+    a.fuel = 2ull * (uint64_t)steps + 16;
     if (a.total == 0) return;
     mark_device_written(out_buf);
 
