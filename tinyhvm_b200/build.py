@@ -23,14 +23,21 @@ FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wno-unuse
          "--expt-relaxed-constexpr", "-Xcudafe", "--diag_suppress=177"]
 
 
-def _newest_header() -> float:
-    hs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.inc")) + [PKG.parent / "include" / "thvm_cuda.h"]
-    return max(h.stat().st_mtime for h in hs)
+def _deps(src: Path, seen=None) -> set:
+    """The files a source includes with quotes, transitively (so that a change to one kernel's .inc rebuilds only it)."""
+    import re
+    seen = set() if seen is None else seen
+    for name in re.findall(r'^\s*#include\s+"([^"]+)"', src.read_text(), flags=re.M):
+        f = (src.parent / name).resolve()
+        if f.exists() and f not in seen:
+            seen.add(f)
+            _deps(f, seen)
+    return seen
 
 
 def _compile(src: Path, verbose_ptxas: bool) -> Path:
     obj = OBJ / (src.stem + ".o")
-    stamp = max(src.stat().st_mtime, _newest_header(), Path(__file__).stat().st_mtime)
+    stamp = max([src.stat().st_mtime, Path(__file__).stat().st_mtime] + [d.stat().st_mtime for d in _deps(src)])
     if obj.exists() and obj.stat().st_mtime >= stamp and not verbose_ptxas:
         return obj
     cmd = [NVCC, *ARCH, *FLAGS, "-c", str(src), "-o", str(obj)]
