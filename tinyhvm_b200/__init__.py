@@ -72,12 +72,18 @@ SYMBOLS = {
     "thvm_cuda_dp_rank": (C.c_int, []),
     "thvm_cuda_dp_allreduce_sum": (C.c_int, [C.POINTER(_u32), C.POINTER(_u64), _u32]),
     "thvm_cuda_dp_shutdown": (None, []),
+    "thvm_cuda_dp_arena_create": (C.c_int, [_u64, _vp]),
+    "thvm_cuda_dp_arena_attach": (C.c_int, [C.c_int, _vp]),
+    "thvm_cuda_dp_sgd_step": (C.c_int, [C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u64), _u32, _u32]),
+    "thvm_cuda_dp_arena_attach_silent": (C.c_int, [C.c_int]),
+    "thvm_cuda_dp_set_poll_limit": (None, [_u64]),
     "thvm_cuda_capture_begin": (C.c_int, []),
     "thvm_cuda_capture_input": (C.c_int, [_u32, _vp, _u64]),
     "thvm_cuda_capture_end": (C.c_int, []),
     "thvm_cuda_graph_set_input": (C.c_int, [C.c_int, C.c_int, _vp]),
     "thvm_cuda_graph_launch": (C.c_int, [C.c_int]),
     "thvm_cuda_graph_result": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),
+    "thvm_cuda_graph_result_async": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),
     "thvm_cuda_graph_counts": (C.c_int, [C.c_int, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u64)]),
     "thvm_cuda_graph_destroy": (None, [C.c_int]),
     "thvm_cuda_maxpool2x2_index": (C.c_int, [_u32, _u32, _u32, _u32, _u32, _u32]),

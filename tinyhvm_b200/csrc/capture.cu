@@ -226,6 +226,18 @@ int thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes) {
     return 0;
 }
 
+// Result `result` of the latest launch, copied to `out` in stream order (after that launch, before any later one) without
+// waiting: the caller reads `out` once the stream has passed this point (an event recorded after the call, or thvm_cuda_sync).
+// Lets a training loop fetch step k's loss while step k + 1 is already running.
+int thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t bytes) {
+    Capture *c = graph_of(graph, "graph_result_async");
+    if (!c) return 1;
+    if (result < 0 || (size_t)result >= c->results.size() || !out) { set_error("graph_result_async: result %d of %zu", result, c->results.size()); return 1; }
+    const Capture::Result &r = c->results[result];
+    THC_CUDA_OK(cudaMemcpyAsync(out, r.host, bytes < r.bytes ? bytes : r.bytes, cudaMemcpyHostToHost, g.stream));
+    return 0;
+}
+
 int thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels) {
     Capture *c = graph_of(graph, "graph_counts");
     if (!c) return 1;

@@ -595,4 +595,5 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) k_g
 #include "gemm_skinny.inc"
 #include "gemm_tma.inc"
 #include "gemm_ta.inc"
+#include "gemm_ps.inc"
 #include "gemm_host.inc"

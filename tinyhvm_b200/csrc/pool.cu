@@ -166,7 +166,7 @@ static void check_device_status(const char *who) {
     THC_CUDA_OK(cudaMemcpyAsync(&st, g.dev_status, sizeof st, cudaMemcpyDeviceToHost, g.stream));
     THC_CUDA_OK(cudaStreamSynchronize(g.stream));
     if (st) {
-        set_error("%s: device status 0x%x (1=load out of bounds, 2=store out of bounds, 4=bad program)", who, st);
+        set_error("%s: device status 0x%x (1=load out of bounds, 2=store out of bounds, 4=bad program, 8=contraction kernel wait ran out, 16=a data-parallel peer never arrived)", who, st);
         THC_CUDA_OK(cudaMemsetAsync(g.dev_status, 0, sizeof(int), g.stream));
     }
 }

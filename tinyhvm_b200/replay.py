@@ -33,6 +33,7 @@ import numpy as np
 from . import abi
 
 (ALLOC, WRITE, READ, DISPATCH, COPY, CONTIGUIFY, FREE, INCREF, DECREF, POOL_RESET, SET_PERSISTENT, ALLREDUCE, MARK) = range(1, 14)
+SGD_FUSED = 100                      # not a trace record: made by fuse_optimizer from an all-reduce and its update dispatches
 TRACE_DIR = Path(__file__).resolve().parent / "traces"
 
 
@@ -139,6 +140,11 @@ class CudaTarget:
         rc = self.lib.thvm_cuda_dp_allreduce_sum((C.c_uint32 * k)(*ids), (C.c_uint64 * k)(*counts), k)
         assert rc == 0, self.be.last_error()
 
+    def sgd_step(self, params, grads, counts, lr_buf):
+        k = len(params)
+        rc = self.lib.thvm_cuda_dp_sgd_step((C.c_uint32 * k)(*params), (C.c_uint32 * k)(*grads), (C.c_uint64 * k)(*counts), k, lr_buf)
+        assert rc == 0, self.be.last_error()
+
 
 class CapturedStep:
     """One steady-state cycle of a trace recorded as a CUDA graph (thvm_cuda_capture_*): `launch(externals)`
@@ -192,6 +198,13 @@ class CapturedStep:
             assert self.lib.thvm_cuda_graph_set_input(self.handle, idx, src.ctypes.data) == 0, self.be.last_error()
         assert self.lib.thvm_cuda_graph_launch(self.handle) == 0, self.be.last_error()
 
+    def results_async(self, outs: dict) -> None:
+        """Queue copies of the named results of the latest launch into the caller's pinned arrays (`outs[name]`);
+        they are valid once the stream has passed this point."""
+        for k, (name, nb) in enumerate(self.reads):
+            if name in outs:
+                assert self.lib.thvm_cuda_graph_result_async(self.handle, k, outs[name].ctypes.data, min(nb, outs[name].nbytes)) == 0, self.be.last_error()
+
     def results(self) -> dict:
         out = {}
         for k, (name, nb) in enumerate(self.reads):
@@ -207,15 +220,65 @@ class CapturedStep:
             self.handle = 0
 
 
+def fuse_optimizer(recs: list[Record]) -> list[Record]:
+    """Rewrite the optimizer tail of a recorded step for `thvm_cuda_dp_sgd_step`.
+
+    The staged step ends with the gradient all-reduce followed, per parameter tensor, by the dispatch
+    T = p - g * lr and the ASSIGN copy p <- T (src/interact/tensor_ops.c:93-147).  Where exactly that shape is found —
+    every all-reduced gradient feeds one such dispatch, whose result is copied over its first leaf — the all-reduce,
+    the dispatches and the copies are replaced by ONE fused record (parameter ids, gradient ids, counts, the buffer
+    holding lr), placed where the last copy stood.  Allocations, constant writes and frees stay as recorded, so buffer
+    ids keep matching.  Anything else is returned unchanged."""
+    ar = [k for k, r in enumerate(recs) if r.op == ALLREDUCE]
+    if len(ar) != 1:
+        return recs
+    grads, counts = recs[ar[0]].f
+    want = {g: n for g, n in zip(grads, counts)}
+    found, drop, last = {}, {ar[0]}, None
+    k = ar[0] + 1
+    while k < len(recs):
+        r = recs[k]
+        if r.op == DISPATCH:
+            a = DispatchArgs(r.blob)
+            ops = [(a.ops[i].uop, a.ops[i].arg_a, a.ops[i].arg_b) for i in range(a.n_ops)]
+            if a.n == 3 and ops == [(abi.MUL, 1, 2), (abi.SUB, 0, 3)] and not a.has_red and a.ids[1] in want and a.ids[1] not in found:
+                numel = 1
+                for d in range(a.full.rank):
+                    numel *= a.full.dims[d]
+                flat = all(a.views[i].contiguous and a.views[i].offset == 0 for i in range(2)) and a.views[2].offset == 0 and \
+                    all(a.views[2].strides[d] == 0 or a.views[2].shape.dims[d] == 1 for d in range(a.views[2].shape.rank))
+                nxt = next((j for j in range(k + 1, len(recs)) if recs[j].op in (COPY, DISPATCH, ALLREDUCE)), None)
+                if flat and numel == want[a.ids[1]] and nxt is not None and recs[nxt].op == COPY and recs[nxt].f[0] == a.ids[0] \
+                        and recs[nxt].f[1] == a.out and recs[nxt].f[2] == 4 * numel:
+                    found[a.ids[1]] = (a.ids[0], a.ids[2])
+                    drop |= {k, nxt}
+                    last = nxt
+        k += 1
+    if set(found) != set(want) or last is None or len({lr for _, lr in found.values()}) < 1:
+        return recs
+    params = tuple(found[g][0] for g in grads)
+    lr_buf = found[grads[-1]][1]          # every tensor's step size is the same external; the last one written is live at the fused call
+    out = []
+    for k, r in enumerate(recs):
+        if k == last:
+            out.append(Record(SGD_FUSED, (params, tuple(grads), tuple(counts), lr_buf)))
+        elif k not in drop:
+            out.append(r)
+    return out
+
+
 class Replayer:
     """Binds a trace to a target once; `run(cycle, externals)` then replays one cycle.
 
     `externals[name]` is a numpy array, or a list of arrays consumed in order when
-    the cycle writes that name several times."""
+    the cycle writes that name several times.  `fused_optimizer=True` replays the optimizer tail of every step
+    through one fused all-reduce + SGD call (see fuse_optimizer)."""
 
-    def __init__(self, target, recs: list[Record]):
+    def __init__(self, target, recs: list[Record], fused_optimizer: bool = False):
         self.t = target
         self.prefix, self.cycles = split_steps(recs)
+        if fused_optimizer:
+            self.cycles = [fuse_optimizer(c) for c in self.cycles]
         self._bound = {}
 
     def _bind(self, recs):
@@ -251,6 +314,8 @@ class Replayer:
                 prog.append(("call", t.set_persistent, tuple(r.f), None))
             elif r.op == ALLREDUCE:
                 prog.append(("call", t.allreduce, tuple(r.f), None))
+            elif r.op == SGD_FUSED:
+                prog.append(("call", t.sgd_step, tuple(r.f), None))
             elif r.op == MARK and r.f[0].startswith("read:"):
                 pending = r.f[0][5:]
         self._bound[key] = prog
