@@ -39,6 +39,34 @@ TinyHVM *thvm_init(const char *device) {
     return ctx;
 }
 
+/* ------------------------------------------------------------------ the reference's lowerer at the vtable boundary
+ * A dispatch in the form dispatch_kernel_rs receives (views, trackers, ops, iteration shape, reduce spec, dtypes) is put
+ * into a KernelEntry and lowered by the reference's own thvm_lower_kernel_uop (src/lower/_.c:765-973), the way
+ * thvm_sched_dispatch_kernel does before it calls dispatch_uop_kernel (src/schedule/_.c:2343-2378).  Returns 1 when a
+ * program was produced.  The output dtype is f32 (the scheduler takes it from the output tensor). */
+int drv_lower_dispatch(const View *const *views, const ShapeTracker *const *sts, u32 n_leaves, const FusedOp *ops, u32 n_ops,
+                       const Shape *full, const ReduceSpec *red, const u32 *leaf_dtypes, UOpKernel *out) {
+    static TinyHVM *lctx = NULL;
+    static KernelEntry ke;
+    if (!lctx) lctx = thvm_init_base("cpu");
+    if (!lctx || n_leaves > FUSE_MAX_LEAVES || n_ops > FUSE_MAX_OPS) return 0;
+    memset(&ke, 0, sizeof ke);
+    for (u32 i = 0; i < n_ops; i++) ke.ops[i] = ops[i];
+    ke.n_ops = n_ops;
+    for (u32 i = 0; i < n_leaves; i++) {
+        ke.leaf_ids[i] = 0xFFFFFFFFu; ke.leaf_kinds[i] = KERNEL_LEAF_TENSOR;
+        ke.leaf_dtypes[i] = leaf_dtypes ? leaf_dtypes[i] : DTYPE_F32;
+        ke.leaf_views[i] = *views[i];
+        if (sts && sts[i]) ke.leaf_sts[i] = *sts[i];
+        else { ke.leaf_sts[i].views[0] = *views[i]; ke.leaf_sts[i].n_views = 1; }
+    }
+    ke.n_leaves = n_leaves;
+    ke.full_shape = *full; ke.raw_out_shape = *full; ke.out_shape = *full;
+    if (red && red->reduce_type) { ke.reduce = *red; ke.has_reduce = red->reduce_type; }
+    ke.output_tid = 0xFFFFFFFFu; ke.raw_output_tid = 0xFFFFFFFFu;
+    return thvm_lower_kernel_uop(lctx, &ke, out, NULL);
+}
+
 /* ------------------------------------------------------------------ results */
 #define DRV_MAX 512
 static struct { char name[64]; f32 *data; u32 n; } drv_res[DRV_MAX];

@@ -120,7 +120,38 @@ static void keepf(TinyHVM *ctx, const char *fmt, u32 step, Term t) { char nm[64]
 /* params (flat, in this order): W1[6,1,5,5] b1[6] W2[16,6,5,5] b2[16] W3[400,120] b3[120] W4[120,84] b4[84] W5[84,10] b5[10]
  * x[steps][B,1,28,28], labels[steps][B].  Keeps the loss of every step, the
  * gradients of step 0 and the parameters after the last step. */
+/* replace the kept tensor `name` by host values (the loss of a captured step is known only after its replay) */
+static void keep_host(const char *name, const f32 *v, u32 n) {
+    for (u32 i = 0; i < drv_n; i++)
+        if (strcmp(drv_res[i].name, name) == 0) { free(drv_res[i].data); drv_res[i].data = malloc((size_t)n * 4); memcpy(drv_res[i].data, v, (size_t)n * 4); drv_res[i].n = n; return; }
+    if (drv_n >= DRV_MAX) return;
+    snprintf(drv_res[drv_n].name, sizeof drv_res[drv_n].name, "%s", name);
+    drv_res[drv_n].data = malloc((size_t)n * 4); memcpy(drv_res[drv_n].data, v, (size_t)n * 4); drv_res[drv_n].n = n; drv_n++;
+}
+
+/* capture_at < steps: step `capture_at` is issued between jit_begin_capture and jit_end_capture (the reference's own
+ * capture / replay entry points, bound by the CUDA hub) and every step from there on is a jit_replay with that step's
+ * batch and one-hot labels set as inputs: the live reference host (reducer, fuser, scheduler) records the step once and
+ * is out of the loop afterwards. */
+static int drv_lenet_impl(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 keep_grads, u32 capture_at);
 int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 keep_grads) {
+    return drv_lenet_impl(dev, B, steps, lr, x, labels, params, keep_grads, 0xFFFFFFFFu);
+}
+int drv_lenet_captured(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 capture_at) {
+    return drv_lenet_impl(dev, B, steps, lr, x, labels, params, 0, capture_at);
+}
+
+/* point the captured step's inputs at step s's data: the batch by its size, the one-hot label matrices by theirs */
+static void lenet_set_inputs(u32 B, const f32 *xs, const f32 *oh) {
+    for (u32 k = 0; k < jit_input_count(); k++) {
+        const u64 nb = jit_input_bytes(k);
+        if (nb == (u64)B * 784 * 4) jit_set_input(k, xs);
+        else if (nb == (u64)B * 10 * 4) jit_set_input(k, oh);
+        else { fprintf(stderr, "drv_lenet_captured: input %u of %llu bytes is neither the batch nor the labels\n", k, (unsigned long long)nb); exit(1); }
+    }
+}
+
+static int drv_lenet_impl(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 *labels, const f32 *params, u32 keep_grads, u32 capture_at) {
     cpu_masked_leaf_workaround(dev);
     TinyHVM *ctx = thvm_init(dev);
     drv_ctx = ctx;
@@ -135,11 +166,23 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
     Term W5 = PARAM("W5", 840, 84, 10),        b5 = PARAM("b5", 10, 10);
     u32 keep_id = ctx->tensor_count;
     double t0 = now_s();
+    f32 *oh_host = calloc((size_t)B * 10, 4);
     for (u32 s = 0; s < steps; s++) {
+        const u8 *lab = labels + (size_t)s * B;
+        if (s > capture_at) {                                                /* replay of the captured step on this step's data */
+            char nm[32]; f32 lv = 0;
+            memset(oh_host, 0, (size_t)B * 10 * 4);
+            for (u32 i = 0; i < B; i++) oh_host[i * 10 + lab[i]] = 1.0f;
+            lenet_set_inputs(B, x + (size_t)s * B * 784, oh_host);
+            jit_replay();
+            jit_result(0, &lv, 4);                                           /* waits for the step */
+            snprintf(nm, sizeof nm, "loss%u", s); keep_host(nm, &lv, 1);
+            continue;
+        }
+        if (s == capture_at) jit_begin_capture(keep_id);
         rec_mark("step_begin");
         rec_note("x", 0);
         Term tx = thvm_tensor(ctx, x + (size_t)s * B * 784, SHAPE(B, 1, 28, 28));
-        const u8 *lab = labels + (size_t)s * B;
         /* forward */
         Term xp = pad_hw(ctx, tx, 2);                                        /* [B,1,32,32] */
         Term u1 = conv_fwd(ctx, xp, W1, b1);                                 /* [B,6,28,28] */
@@ -195,8 +238,19 @@ int drv_lenet(const char *dev, u32 B, u32 steps, f32 lr, const f32 *x, const u8 
         rec_mark("read:b5");
         f32 *sync = thvm_to_host(ctx, b5); (void)sync;                       /* drain the device queue before the clock stops */
         rec_mark("step_end");
-        if (s + 1 < steps) { thvm_reset(ctx, keep_id); thvm_sched_reset_runtime(); }
+        if (s + 1 < steps || s == capture_at) { thvm_reset(ctx, keep_id); thvm_sched_reset_runtime(); }
+        if (s == capture_at) {                                               /* nothing of the step has run yet: run it now */
+            char nm[32]; f32 lv = 0;
+            jit_end_capture();
+            memset(oh_host, 0, (size_t)B * 10 * 4);
+            for (u32 i = 0; i < B; i++) oh_host[i * 10 + lab[i]] = 1.0f;
+            lenet_set_inputs(B, x + (size_t)s * B * 784, oh_host);
+            jit_replay();
+            jit_result(0, &lv, 4);
+            snprintf(nm, sizeof nm, "loss%u", s); keep_host(nm, &lv, 1);
+        }
     }
+    free(oh_host);
     drv_secs = now_s() - t0;
     keep(ctx, "W1", W1); keep(ctx, "b1", b1); keep(ctx, "W2", W2); keep(ctx, "b2", b2); keep(ctx, "W3", W3);
     keep(ctx, "b3", b3); keep(ctx, "W4", W4); keep(ctx, "b4", b4); keep(ctx, "W5", W5); keep(ctx, "b5", b5);

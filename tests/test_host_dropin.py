@@ -199,3 +199,19 @@ def test_lowered_kop_programs_cuda_vs_cpu(monkeypatch):
     A, B = (synth.normal(synth.SEED_BASE + 3, t, n * n) / np.float32(np.sqrt(n)) for t in range(2))
     compare_runs("drv_gemm", (n, A, B), 1e-4)
     compare_runs("drv_mlp", mlp_inputs(B=16, I=64, H=32), 1e-4)
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_lenet_step_captured_by_the_live_host_and_replayed():
+    """The reference's own capture / replay entry points (jit_begin_capture / jit_end_capture / jit_replay,
+    src/tinyhvm.h:1294-1300), bound by the CUDA hub: the live reference host issues step 2 between begin and end, and
+    steps 2..5 are replays of the recorded step on fresh batches.  Losses and final parameters as in the eager run."""
+    B, steps = 8, 6
+    x, lab, ps = lenet_inputs(B, steps)
+    eager = hostref.run("drv_lenet", "cuda", B, steps, 0.01, x, lab, np.concatenate(ps), 0)
+    cap = hostref.run("drv_lenet_captured", "cuda", B, steps, 0.01, x, lab, np.concatenate(ps), 2)
+    for s in range(steps):
+        assert abs(cap[f"loss{s}"][0] - eager[f"loss{s}"][0]) < 2e-5, (s, cap[f"loss{s}"][0], eager[f"loss{s}"][0])
+    for n in LENET_NAMES:
+        assert np.allclose(cap[n], eager[n], rtol=1e-5, atol=1e-6), n

@@ -108,4 +108,52 @@ static TinyHVM *thvm_init_device(TinyHVM *(*base_init)(const char *), const char
     return ctx;
 }
 
+// ---- step capture / replay: the reference's JIT entry points (src/tinyhvm.h:1294-1300), which it declares for Apple
+// builds only and implements in src/backend/metal/jit.m:24-631.  Same call sequence as there (test/archive/test_jit_dense.m):
+//     jit_begin_capture(n_persistent);  <one training step through thvm_eval / thvm_reduce>;  jit_end_capture();
+//     then per step: refresh the inputs, jit_replay().
+// Differences a driver has to know: the captured step is recorded, not run (its first execution is the first
+// jit_replay; values read inside it come back as zeros and are fetched afterwards with jit_result), the step must have
+// run eagerly before (kernel plans exist) and must free what it allocates (end with thvm_reset).  Per-step data that the
+// step uploads with buf_write (a fresh tensor per batch) becomes an input when it is at least 257 bytes (small writes are
+// shape / axes / scalar constants); jit_set_input points input k at this step's host memory before jit_replay.
+#ifndef __APPLE__
+static int cuda_jit_graph = 0;
+void jit_begin_capture(u32 n_persistent_bufs) {
+    (void)n_persistent_bufs;                       // buffers that exist now are the persistent ones
+    void (*thr)(u64) = cuda_hub_sym("thvm_cuda_capture_input_threshold");
+    int (*begin)(void) = cuda_hub_sym("thvm_cuda_capture_begin");
+    if (cuda_jit_graph) { void (*destroy)(int) = cuda_hub_sym("thvm_cuda_graph_destroy"); destroy(cuda_jit_graph); cuda_jit_graph = 0; }
+    thr(257);
+    if (begin() != 0) { fprintf(stderr, "TinyHVM cuda: jit_begin_capture failed\n"); exit(1); }
+}
+void jit_end_capture(void) {
+    int (*end)(void) = cuda_hub_sym("thvm_cuda_capture_end");
+    void (*thr)(u64) = cuda_hub_sym("thvm_cuda_capture_input_threshold");
+    const char *(*err)(void) = cuda_hub_sym("thvm_cuda_last_error");
+    cuda_jit_graph = end();
+    thr(0);
+    if (!cuda_jit_graph) { fprintf(stderr, "TinyHVM cuda: jit_end_capture: %s\n", err()); exit(1); }
+}
+void jit_flush(void) { void (*sync)(void) = cuda_hub_sym("thvm_cuda_sync"); sync(); }
+void jit_replay(void) {
+    int (*launch)(int) = cuda_hub_sym("thvm_cuda_graph_launch");
+    if (!cuda_jit_graph || launch(cuda_jit_graph) != 0) { fprintf(stderr, "TinyHVM cuda: jit_replay without a captured step\n"); exit(1); }
+}
+// additions of this backend
+u32 jit_input_count(void) {
+    int (*counts)(int, u32 *, u32 *, u64 *) = cuda_hub_sym("thvm_cuda_graph_counts");
+    u32 n = 0; counts(cuda_jit_graph, &n, NULL, NULL); return n;
+}
+u64 jit_input_bytes(u32 k) { u64 (*f)(int, int) = cuda_hub_sym("thvm_cuda_graph_input_bytes"); return f(cuda_jit_graph, (int)k); }
+void jit_set_input(u32 k, const void *host) {
+    int (*f)(int, int, const void *) = cuda_hub_sym("thvm_cuda_graph_set_input");
+    if (f(cuda_jit_graph, (int)k, host) != 0) { fprintf(stderr, "TinyHVM cuda: jit_set_input(%u) failed\n", k); exit(1); }
+}
+void jit_result(u32 k, void *out, u64 bytes) {
+    int (*f)(int, int, void *, u64) = cuda_hub_sym("thvm_cuda_graph_result");
+    if (f(cuda_jit_graph, (int)k, out, bytes) != 0) { fprintf(stderr, "TinyHVM cuda: jit_result(%u) failed\n", k); exit(1); }
+}
+#endif
+
 #endif  // THVM_BACKEND_CUDA_HUB

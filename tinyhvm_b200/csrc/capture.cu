@@ -43,6 +43,7 @@ struct Capture {
 };
 
 static std::vector<Capture *> graphs;              // handle = index + 1
+static uint64_t input_threshold = 0;               // capture: host writes of at least this many bytes count as inputs (0 = only writes above 1 MiB)
 constexpr uint64_t ARENA_CHUNK = 4ull << 20;
 
 bool capturing() { return g.cap != nullptr; }
@@ -54,6 +55,7 @@ void capture_fail(const char *why) {
 }
 
 uint32_t capture_first_id() { return g.cap ? g.cap->first_id : 0; }
+uint64_t capture_input_threshold() { return input_threshold; }
 
 uint8_t *capture_arena_take(uint64_t bytes) {
     Capture &c = *g.cap;
@@ -236,6 +238,17 @@ int thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t byte
     const Capture::Result &r = c->results[result];
     THC_CUDA_OK(cudaMemcpyAsync(out, r.host, bytes < r.bytes ? bytes : r.bytes, cudaMemcpyHostToHost, g.stream));
     return 0;
+}
+
+// A host that writes its per-step data with plain buf_write inside the captured step (the reference's drivers create
+// a fresh tensor per batch) declares by size which writes are data: every buf_write of at least `bytes` bytes made while
+// capturing becomes an input, in call order, as if it had been announced with capture_input.  0 restores the default.
+void thvm_cuda_capture_input_threshold(uint64_t bytes) { input_threshold = bytes; }
+
+uint64_t thvm_cuda_graph_input_bytes(int graph, int input) {
+    Capture *c = graph_of(graph, "graph_input_bytes");
+    if (!c || input < 0 || (size_t)input >= c->inputs.size()) return 0;
+    return c->inputs[input].bytes;
 }
 
 int thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels) {
