@@ -399,15 +399,65 @@ def reference_arm(args, rank: int):
     sec = statistics.mean(times)
     nbytes = (FWD_BYTES + BWD_BYTES) * rows / ROWS
     val = nbytes / sec / 1e9
-    sample = f"{rows} of {ROWS} rows per step (fwd+bwd), {len(times)} steps, single-threaded scalar interpreter"
+    sample = (f"{rows} of {ROWS} rows per step (fwd+bwd), {len(times)} steps, single-threaded scalar interpreter; ms_per_step is the "
+              f"measured time of those rows, extrapolated_ms_per_step the same x{ROWS // rows} for the whole workload")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3 * ROWS / rows, "higher_is_better": True, "scaling": "weak",
+        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "extrapolated_ms_per_step": sec * 1e3 * ROWS / rows,
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": 1, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def cpu_baselines_other_configs(full: bool):
+    """The reference's own CPU backend on the staged drivers of configs 3, 4 and 5 (thvm_init("cpu"), one core: the CPU
+    kernels are single-threaded scalar interpreters).  Bounded sizes by default; `full` runs the sizes of the baseline
+    plan (512^3 and 1024^3 GEMMs, LeNet at batch 1024, the VGG-style net at batch 4), which takes about a quarter of an hour."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import hostref
+    from tinyhvm_b200 import configs, synth
+    if not hostref.available():
+        return {"unavailable": "oracle/_ref/libthvm_host_ref.so not built (needs the reference checkout at build time)"}
+    out = {"cores": 1, "kind": "reference", "backend": 'thvm_init("cpu"), staged drivers'}
+    for n in ((512, 1024) if full else (256,)):
+        A, B = (synth.normal(synth.SEED_BASE + 3, t, n * n) / np.float32(np.sqrt(n)) for t in range(2))
+        sec = hostref.run("drv_gemm", "cpu", n, A, B)["_seconds"]
+        gf = 3 * 2.0 * n ** 3 / sec / 1e9
+        out[f"cfg3_gemm_{n}"] = {"seconds": sec, "gflops": gf, "what": "C=A@B, sum(C*C), dA, dB",
+                                 "extrapolated_seconds_4096": sec * (4096 / n) ** 3, "note": "4096^3 figure is an N^3 extrapolation"}
+    Bl = 1024 if full else 64
+    x, lab, ps = configs.lenet_inputs(Bl, 1)
+    sec = hostref.run("drv_lenet", "cpu", Bl, 1, 0.01, x, lab, np.concatenate(ps), 0)["_seconds"]
+    out["cfg4_lenet"] = {"batch": Bl, "seconds_per_step": sec, "samples_per_s": Bl / sec,
+                         "note": "full config size" if full else "per-sample rate at batch 64 (the interpreter is linear in the batch)"}
+    if full:
+        Bv = 4
+        x, lab, ps = configs.vgg_inputs(Bv, 1)
+        sec = hostref.run("drv_vgg", "cpu", Bv, 64, 100, np.array(configs.VGG_CHAN, np.uint32), 1, 0.01, x, lab, np.concatenate(ps), 0)["_seconds"]
+        out["cfg5_vgg"] = {"batch": Bv, "seconds_per_step": sec, "samples_per_s": Bv / sec,
+                           "extrapolated_seconds_per_step_512": sec * 512 / Bv, "note": "batch 4; the batch-512 figure is a linear extrapolation"}
+    return out
+
+
+def lenet_live_host(B: int = 1024):
+    """Config 4 with the reference's own host in the loop: thvm_init("cuda") + the staged LeNet driver, every step going
+    through interaction-net reduction, fusion, scheduling and the vtable (no trace, no graph).  Seconds per steady-state step
+    = (time of 8 steps - time of 2 steps) / 6."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import hostref
+    from tinyhvm_b200 import configs
+    if not hostref.available():
+        return {"unavailable": "oracle/_ref/libthvm_host_ref.so not built"}
+    res = {}
+    for steps in (2, 8):
+        x, lab, ps = configs.lenet_inputs(B, steps)
+        res[steps] = hostref.run("drv_lenet", "cuda", B, steps, 0.01, x, lab, np.concatenate(ps), 0)["_seconds"]
+    per = (res[8] - res[2]) / 6
+    return {"batch": B, "ms_per_step": per * 1e3, "samples_per_s": B / per, "seconds_2_steps": res[2], "seconds_8_steps": res[8],
+            "path": 'reference host live: thvm_init("cuda"), thvm_eval per realise point, vtable hub'}
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -424,7 +474,7 @@ def main():
     ap.add_argument("--unfused", action="store_true", help="lenet / vgg workloads: optimizer tail as recorded (all-reduce call + one dispatch and copy per parameter tensor)")
     ap.add_argument("--no-sustain", action="store_true", help="skip the ~0.6 s untimed continuation used for clock sampling (profiling runs)")
     ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "lenet", "vgg"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "lenet", "vgg", "lenet_live", "cpu_baselines"],
                     help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet / vgg = only the config-4 / config-5 training steps")
     ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
@@ -435,6 +485,18 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.workload == "cpu_baselines":                  # CPU only: the baseline plan's sizes for configs 3, 4, 5
+        if rank == 0:
+            print(json.dumps({"metric": "cpu_baselines", "unit": "see entries", "n_gpus": 0, "value": None,
+                              "config": {"workload": "reference CPU backend on the staged drivers of configs 3, 4, 5"},
+                              "cpu_baselines": cpu_baselines_other_configs(full=True)}))
+        return
+    if args.workload == "lenet_live":                     # a process of its own: the reference host initialises the library itself
+        if rank == 0:
+            print(json.dumps({"metric": "lenet_train_samples_per_s", "unit": "samples/s", "n_gpus": 1,
+                              "config": {"workload": "cfg4 LeNet-5 SGD step, batch 1024, reference host live on the CUDA backend"},
+                              "live": (r := lenet_live_host()), "value": r.get("samples_per_s")}))
         return
 
     import torch
@@ -554,37 +616,46 @@ def main():
     # ---- end to end with host buffers through the same C ABI
     e2e_steps = max(3, min(args.steps, 5))
 
-    # The rows go through in slices: while slice i is uploaded (buf_write waits for its DMA) and computed, the results of
-    # slice i-1 travel back on the library's copy stream (buf_read_async), so the two PCIe directions overlap.
+    # The rows go through in slices, so that the device works on one slice while the next one is uploaded.
     n_slices = 8 if rows % 8 == 0 and rows >= 64 else 1
     srows = rows // n_slices
     s_fwd, s_bwd = chain_dispatches(srows, COLS, [x[: srows * COLS] for x in arrays])
     s_ids = [[be.alloc(srows * COLS * 4) for _ in range(3)] for _ in range(n_slices)]
     s_out = [(be.alloc(srows * 4), be.alloc(srows * COLS * 4)) for _ in range(n_slices)]
 
-    def e2e_step():
+    def e2e_step(overlap_reads: bool):
+        """vtable slots only (buf_write, dispatch_kernel_rs, buf_read) — what a reference host can reach — or, with
+        `overlap_reads`, the read-backs through the library's extra buf_read_async, which lets slice i's results travel
+        while slice i + 1 is uploaded."""
         for s in range(n_slices):
             lo = s * srows * COLS
             for i, a in zip(s_ids[s], arrays):
                 lib.thvm_cuda_buf_write(i, a[lo: lo + srows * COLS].ctypes.data, srows * COLS * 4)
             be.dispatch_ids(s_out[s][0], s_ids[s], s_fwd)
             be.dispatch_ids(s_out[s][1], s_ids[s] + [zero_id], s_bwd)
-            lib.thvm_cuda_buf_read_async(s_out[s][1], g_host.data_ptr() + lo * 4, srows * COLS * 4)
-            lib.thvm_cuda_buf_read_async(s_out[s][0], y_host.data_ptr() + s * srows * 4, srows * 4)
+            read = lib.thvm_cuda_buf_read_async if overlap_reads else lib.thvm_cuda_buf_read
+            read(s_out[s][1], g_host.data_ptr() + lo * 4, srows * COLS * 4)
+            read(s_out[s][0], y_host.data_ptr() + s * srows * 4, srows * 4)
         lib.thvm_cuda_sync()
 
-    e2e_step()
-    barrier()
-    w0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    def time_e2e(overlap_reads: bool):
+        e2e_step(overlap_reads)
+        barrier()
+        w0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step(overlap_reads)
+        barrier()
+        ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    e2e_ms = time_e2e(False)
+    e2e_async_ms = time_e2e(True)
     e2e_val = world * (fwd_bytes + bwd_bytes) / (e2e_ms * 1e-3) / 1e9
+    e2e_async_val = world * (fwd_bytes + bwd_bytes) / (e2e_async_ms * 1e-3) / 1e9
 
     # ---- checks on the result of the timed runs (size-independent properties)
     y = y_host.numpy()
@@ -634,7 +705,10 @@ def main():
                 "ms_per_step": sustained_ms, "steps": cont_steps, "value": world * (fwd_bytes + bwd_bytes) / (sustained_ms * 1e-3) / 1e9,
                 "note": "untimed continuation of the same loop (~0.6 s) over which the clocks were sampled"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(sum(x.nbytes for x in arrays)),
-                    "d2h_bytes_per_step": int(g_host.numel() * 4 + y_host.numel() * 4), "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "d2h_bytes_per_step": int(g_host.numel() * 4 + y_host.numel() * 4), "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "api": "vtable slots only: buf_write, dispatch_kernel_rs, buf_read"},
+            "e2e_overlapped_reads": {"value": e2e_async_val, "unit": UNIT, "ms_per_step": e2e_async_ms,
+                                     "api": "same, read-backs through the library's extra thvm_cuda_buf_read_async"},
             "gpu_launches": int(launches),
             "roofline": roof(dom), "roofline_other": roof(oth),
             "checks": {"y_rows0_3_vs_f64": bool(ok_y), "g_rows0_3_bit_exact": bool(ok_g), "backend_error": err},
@@ -642,6 +716,14 @@ def main():
         line["extras"] = {"cfg4_lenet_train": lenet, "cfg5_vgg_train": vgg}
         if world == 1 and rows == ROWS and not args.no_extras:
             line["extras"]["cfg3_gemm_4096"] = gemm_section(be, stream, 4096)
+        if world == 1 and rows == ROWS and not args.no_extras:
+            try:                                           # the live reference host needs the library to itself: own process
+                r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--workload", "lenet_live"], capture_output=True, text=True, timeout=600)
+                line["extras"]["cfg4_lenet_live_host"] = json.loads(r.stdout.strip().splitlines()[-1])["live"]
+            except Exception as ex:
+                line["extras"]["cfg4_lenet_live_host"] = {"error": repr(ex)}
+            if not args.no_cpu_baseline:
+                line["extras"]["cpu_baselines"] = cpu_baselines_other_configs(full=False)
         if not args.no_cpu_baseline and world == 1:
             sample_rows = 512
             sec, kind = cpu_run(sample_rows, [x[: sample_rows * COLS] for x in arrays], repeat=2)

@@ -286,9 +286,10 @@ int      thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes
 int      thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t bytes);
 int      thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels);
 /* For hosts that upload their per-step data with plain buf_write inside the step (the reference's drivers make a fresh
- * tensor per batch): while capturing, every buf_write of at least `bytes` bytes is an input, in call order (0 = only
- * writes above 1 MiB, the default).  graph_input_bytes tells the inputs apart afterwards. */
-void     thvm_cuda_capture_input_threshold(uint64_t bytes);
+ * tensor per batch): the byte sizes of those uploads, declared before capture_begin.  While capturing, a buf_write of
+ * exactly one of these sizes is an input, in call order; every other staged write stays a constant of the step (n = 0
+ * clears the list, at most 8 sizes).  graph_input_bytes tells the inputs apart afterwards. */
+void     thvm_cuda_capture_input_sizes(const uint64_t *sizes, uint32_t n);
 uint64_t thvm_cuda_graph_input_bytes(int graph, int input);
 void     thvm_cuda_graph_destroy(int graph);
 

@@ -179,7 +179,7 @@ static int drv_lenet_impl(const char *dev, u32 B, u32 steps, f32 lr, const f32 *
             snprintf(nm, sizeof nm, "loss%u", s); keep_host(nm, &lv, 1);
             continue;
         }
-        if (s == capture_at) jit_begin_capture(keep_id);
+        if (s == capture_at) { jit_declare_input((u64)B * 784 * 4); jit_declare_input((u64)B * 10 * 4); jit_begin_capture(keep_id); }
         rec_mark("step_begin");
         rec_note("x", 0);
         Term tx = thvm_tensor(ctx, x + (size_t)s * B * 784, SHAPE(B, 1, 28, 28));

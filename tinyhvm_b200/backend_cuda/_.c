@@ -115,24 +115,27 @@ static TinyHVM *thvm_init_device(TinyHVM *(*base_init)(const char *), const char
 // Differences a driver has to know: the captured step is recorded, not run (its first execution is the first
 // jit_replay; values read inside it come back as zeros and are fetched afterwards with jit_result), the step must have
 // run eagerly before (kernel plans exist) and must free what it allocates (end with thvm_reset).  Per-step data that the
-// step uploads with buf_write (a fresh tensor per batch) becomes an input when it is at least 257 bytes (small writes are
-// shape / axes / scalar constants); jit_set_input points input k at this step's host memory before jit_replay.
+// step uploads with buf_write (a fresh tensor per batch) is declared by its byte size with jit_declare_input before
+// jit_begin_capture; jit_set_input points input k at this step's host memory before jit_replay.
 #ifndef __APPLE__
 static int cuda_jit_graph = 0;
+static u64 cuda_jit_sizes[8];
+static u32 cuda_jit_n_sizes = 0;
+void jit_declare_input(u64 bytes) { if (cuda_jit_n_sizes < 8) cuda_jit_sizes[cuda_jit_n_sizes++] = bytes; }   // addition of this backend
 void jit_begin_capture(u32 n_persistent_bufs) {
     (void)n_persistent_bufs;                       // buffers that exist now are the persistent ones
-    void (*thr)(u64) = cuda_hub_sym("thvm_cuda_capture_input_threshold");
+    void (*sizes)(const u64 *, u32) = cuda_hub_sym("thvm_cuda_capture_input_sizes");
     int (*begin)(void) = cuda_hub_sym("thvm_cuda_capture_begin");
     if (cuda_jit_graph) { void (*destroy)(int) = cuda_hub_sym("thvm_cuda_graph_destroy"); destroy(cuda_jit_graph); cuda_jit_graph = 0; }
-    thr(257);
+    sizes(cuda_jit_sizes, cuda_jit_n_sizes);
     if (begin() != 0) { fprintf(stderr, "TinyHVM cuda: jit_begin_capture failed\n"); exit(1); }
 }
 void jit_end_capture(void) {
     int (*end)(void) = cuda_hub_sym("thvm_cuda_capture_end");
-    void (*thr)(u64) = cuda_hub_sym("thvm_cuda_capture_input_threshold");
+    void (*sizes)(const u64 *, u32) = cuda_hub_sym("thvm_cuda_capture_input_sizes");
     const char *(*err)(void) = cuda_hub_sym("thvm_cuda_last_error");
     cuda_jit_graph = end();
-    thr(0);
+    sizes(NULL, 0); cuda_jit_n_sizes = 0;
     if (!cuda_jit_graph) { fprintf(stderr, "TinyHVM cuda: jit_end_capture: %s\n", err()); exit(1); }
 }
 void jit_flush(void) { void (*sync)(void) = cuda_hub_sym("thvm_cuda_sync"); sync(); }

@@ -43,7 +43,8 @@ struct Capture {
 };
 
 static std::vector<Capture *> graphs;              // handle = index + 1
-static uint64_t input_threshold = 0;               // capture: host writes of at least this many bytes count as inputs (0 = only writes above 1 MiB)
+static uint64_t input_sizes[8];                    // capture: host writes of exactly these sizes count as inputs (beside writes above 1 MiB)
+static uint32_t n_input_sizes = 0;
 constexpr uint64_t ARENA_CHUNK = 4ull << 20;
 
 bool capturing() { return g.cap != nullptr; }
@@ -55,7 +56,7 @@ void capture_fail(const char *why) {
 }
 
 uint32_t capture_first_id() { return g.cap ? g.cap->first_id : 0; }
-uint64_t capture_input_threshold() { return input_threshold; }
+bool capture_write_is_input(uint64_t bytes) { for (uint32_t i = 0; i < n_input_sizes; i++) if (input_sizes[i] == bytes) return true; return false; }
 
 uint8_t *capture_arena_take(uint64_t bytes) {
     Capture &c = *g.cap;
@@ -240,10 +241,14 @@ int thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t byte
     return 0;
 }
 
-// A host that writes its per-step data with plain buf_write inside the captured step (the reference's drivers create
-// a fresh tensor per batch) declares by size which writes are data: every buf_write of at least `bytes` bytes made while
-// capturing becomes an input, in call order, as if it had been announced with capture_input.  0 restores the default.
-void thvm_cuda_capture_input_threshold(uint64_t bytes) { input_threshold = bytes; }
+// A host that uploads its per-step data with plain buf_write inside the captured step (the reference's drivers create a
+// fresh tensor per batch) declares the byte sizes of those uploads: while capturing, every buf_write of exactly one of
+// these sizes becomes an input, in call order, as if it had been announced with capture_input; all other staged writes
+// stay constants of the step.  n = 0 clears the list.
+void thvm_cuda_capture_input_sizes(const uint64_t *sizes, uint32_t n) {
+    n_input_sizes = n > 8 ? 8 : n;
+    for (uint32_t i = 0; i < n_input_sizes; i++) input_sizes[i] = sizes[i];
+}
 
 uint64_t thvm_cuda_graph_input_bytes(int graph, int input) {
     Capture *c = graph_of(graph, "graph_input_bytes");

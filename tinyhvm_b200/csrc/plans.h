@@ -12,6 +12,8 @@ enum PlanKind : int {
     PLAN_CONTRACT,      // SUM(MUL(a,b)) with separable operands -> GEMM (gemm.cu)
     PLAN_POOL,          // RMAX over the 2x2 windows of contiguous planes -> pooling kernel (uop.cu)
     PLAN_POOL_BWD,      // the mask-form gradient of that pool -> pooling backward kernel (uop.cu)
+    PLAN_PAD2D,         // padding of contiguous planes materialised (layout.cu)
+    PLAN_WIN2PLANE,     // 2x2-window layout copied back to plane layout (layout.cu)
 };
 
 struct FastDesc;        // family-specific, defined in fast_desc.h
@@ -43,5 +45,10 @@ bool try_pool2x2(Plan *p);
 bool launch_pool2x2(Plan *p, const GenArgs &args);
 bool try_pool2x2_bwd(Plan *p);
 bool launch_pool2x2_bwd(Plan *p, const GenArgs &args);
+// layout-changing copies (layout.cu)
+bool try_pad2d(Plan *p);
+bool launch_pad2d(Plan *p, const GenArgs &args);
+bool try_window_to_plane(Plan *p);
+bool launch_window_to_plane(Plan *p, const GenArgs &args);
 
 }  // namespace thc

@@ -357,7 +357,7 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
             b.zero_pending = false;
         }
     }
-    if (g.cap && capture_input_threshold() && bytes >= capture_input_threshold()) { capture_add_input(b.ptr, data, bytes); return; }
+    if (g.cap && capture_write_is_input(bytes)) { capture_add_input(b.ptr, data, bytes); return; }
     if (bytes <= RING_MAX_MSG) {
         uint8_t *stage = ring_take(bytes);
         memcpy(stage, data, bytes);

@@ -106,7 +106,7 @@ bool capturing();
 // mark the running capture unusable (capture_end will then fail with this reason); no-op outside a capture
 void capture_fail(const char *why);
 uint32_t capture_first_id();                                    // first buffer id handed out inside the capture
-uint64_t capture_input_threshold();                             // host writes of at least this size made inside a capture are inputs (0: none by size)
+bool capture_write_is_input(uint64_t bytes);                    // a host write of this size made inside a capture is per-step data, not a constant
 uint8_t *capture_arena_take(uint64_t bytes);                    // pinned host memory that lives as long as the graph
 int  capture_add_input(void *dst, const void *src, uint64_t bytes);
 void capture_add_result(const void *src, uint64_t bytes);
