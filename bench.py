@@ -262,6 +262,11 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     else:
         graph = rp.capture(rp.cycles[1], ext(0))           # the steady-state step as one CUDA graph launch
         graph.launch(ext(3)); losses.append(float(graph.results()["loss"][0]))
+        ab, au, bt = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        na, npool = C.c_uint32(), C.c_uint32()
+        be.lib.thvm_cuda_graph_memory(graph.handle, C.byref(ab), C.byref(au), C.byref(na), C.byref(npool), C.byref(bt))
+        split["memory_plan"] = {"arena_bytes": ab.value, "arena_bytes_used": au.value, "buffers_in_arena": na.value,
+                                "buffers_left_to_allocator": npool.value, "bytes_requested_per_step": bt.value}
         # ---- where a step's time goes: device time of one graph launch (events around it, host waits each time)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         dev_ms = []

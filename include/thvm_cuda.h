@@ -292,6 +292,14 @@ int      thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_resul
 void     thvm_cuda_capture_input_sizes(const uint64_t *sizes, uint32_t n);
 uint64_t thvm_cuda_graph_input_bytes(int graph, int input);
 void     thvm_cuda_graph_destroy(int graph);
+/* Memory plan of a captured step.  The buffers a captured step allocates are placed at offsets of ONE arena by replaying
+ * the step's alloc / free order (liveness) through a first-fit free list — the counterpart of the scheduler's slot plan
+ * (src/schedule/_.c:2017-2112) and of the Metal backend's step planner (src/backend/metal/pool.m:225-378) — so the
+ * recorded graph contains no allocation or free nodes.  The arena is sized from the peak of the last eager step (which
+ * ended with pool_reset); buffers that do not fit fall back to stream-ordered allocations inside the graph.  Reports: arena
+ * size, highest offset used, buffers placed in the arena, buffers left to the pool, sum of all bytes requested. */
+int      thvm_cuda_graph_memory(int graph, uint64_t *arena_bytes, uint64_t *arena_used, uint32_t *arena_buffers,
+                                uint32_t *pool_buffers, uint64_t *bytes_requested);
 
 /* ---- index-producing kernels (integer outputs, bit-exact) ----
  * 2x2 stride-2 max-pool of `planes` contiguous [H, W] f32 planes: values to `out_val`

@@ -35,6 +35,15 @@ struct Capture {
     std::vector<Result> results;
     uint64_t launches = 0, launches_at_begin = 0;
     uint32_t first_id = 0;
+    // Step planner (the counterpart of the slot plan the reference's scheduler makes from liveness, src/schedule/_.c:2017-2112,
+    // and of the Metal backend's step planner, src/backend/metal/pool.m:225-378): every buffer the captured step allocates
+    // gets an offset in ONE arena instead of a stream-ordered allocation.  The step's alloc / free calls arrive in the
+    // order the single stream will run the work, so a block may be handed out again as soon as the step has freed it:
+    // a first-fit free list replays the liveness.  The recorded graph then holds no allocation or free nodes at all.
+    uint8_t *arena = nullptr;
+    uint64_t arena_bytes = 0, arena_high = 0, arena_served = 0;       // size, highest offset used, bytes handed out in total
+    uint32_t arena_allocs = 0, pool_allocs = 0;                        // buffers placed in the arena / left to the pool (arena full)
+    std::vector<std::pair<uint64_t, uint64_t>> free_list;              // (offset, bytes), sorted by offset
     // host-side state of every buffer that existed when the capture began, put back if the capture is refused
     struct Snap { uint32_t id; void *ptr; uint32_t refcount; bool shadow_valid, zero_pending, plain_alloc; uint8_t shadow[256]; };
     std::vector<Snap> snaps;
@@ -56,6 +65,37 @@ void capture_fail(const char *why) {
 }
 
 uint32_t capture_first_id() { return g.cap ? g.cap->first_id : 0; }
+
+void *capture_arena_alloc(uint64_t bytes) {
+    if (!g.cap || !g.cap->arena) return nullptr;
+    Capture &c = *g.cap;
+    const uint64_t need = (bytes + 255) & ~255ull;
+    for (size_t i = 0; i < c.free_list.size(); i++) {
+        if (c.free_list[i].second < need) continue;
+        const uint64_t off = c.free_list[i].first;
+        if (c.free_list[i].second == need) c.free_list.erase(c.free_list.begin() + (long)i);
+        else { c.free_list[i].first += need; c.free_list[i].second -= need; }
+        if (off + need > c.arena_high) c.arena_high = off + need;
+        c.arena_served += need; c.arena_allocs++;
+        return c.arena + off;
+    }
+    c.pool_allocs++;
+    return nullptr;
+}
+
+void capture_arena_give_back(void *ptr, uint64_t bytes) {
+    Capture &c = *g.cap;
+    const uint64_t off = (uint64_t)((uint8_t *)ptr - c.arena), need = (bytes + 255) & ~255ull;
+    size_t i = 0;
+    while (i < c.free_list.size() && c.free_list[i].first < off) i++;
+    c.free_list.insert(c.free_list.begin() + (long)i, {off, need});
+    if (i + 1 < c.free_list.size() && c.free_list[i].first + c.free_list[i].second == c.free_list[i + 1].first) {
+        c.free_list[i].second += c.free_list[i + 1].second; c.free_list.erase(c.free_list.begin() + (long)i + 1);
+    }
+    if (i > 0 && c.free_list[i - 1].first + c.free_list[i - 1].second == c.free_list[i].first) {
+        c.free_list[i - 1].second += c.free_list[i].second; c.free_list.erase(c.free_list.begin() + (long)i);
+    }
+}
 bool capture_write_is_input(uint64_t bytes) { for (uint32_t i = 0; i < n_input_sizes; i++) if (input_sizes[i] == bytes) return true; return false; }
 
 uint8_t *capture_arena_take(uint64_t bytes) {
@@ -106,6 +146,7 @@ static void destroy(Capture *c) {
     if (c->exec) cudaGraphExecDestroy(c->exec);
     if (c->graph) cudaGraphDestroy(c->graph);
     for (uint8_t *p : c->chunks) cudaFreeHost(p);
+    if (c->arena) cudaFree(c->arena);
     delete c;
 }
 
@@ -146,8 +187,14 @@ int thvm_cuda_capture_begin(void) {
         if (b.shadow) memcpy(sn.shadow, b.shadow, sizeof sn.shadow);
         c->snaps.push_back(sn);
     }
+    // the arena: what the last finished step held at its peak, plus room for the holes a first-fit replay leaves
+    if (g.last_step_peak) {
+        c->arena_bytes = g.last_step_peak + g.last_step_peak / 4 + (64ull << 20);
+        if (cudaMalloc((void **)&c->arena, c->arena_bytes) != cudaSuccess) { cudaGetLastError(); c->arena = nullptr; c->arena_bytes = 0; }
+        else c->free_list.push_back({0, c->arena_bytes});
+    }
     cudaError_t e = cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed);
-    if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_begin: %s", cudaGetErrorString(e)); delete c; return 1; }
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_begin: %s", cudaGetErrorString(e)); destroy(c); return 1; }
     g.cap = c;
     return 0;
 }
@@ -164,7 +211,7 @@ int thvm_cuda_capture_end(void) {
     if (!g.cap) { set_error("capture_end: no capture is running"); return 0; }
     Capture *c = g.cap;
     for (uint32_t i = c->first_id; i < THC_MAX_BUFS && !c->failed; i++)
-        if (g.bufs[i].live && g.bufs[i].ptr && !g.bufs[i].plain_alloc)
+        if (g.bufs[i].live && g.bufs[i].ptr && !g.bufs[i].plain_alloc)     // (a buffer in the step arena counts too: its memory is the graph's)
             capture_fail("a buffer allocated inside the captured step is still live: the step must free what it allocates (end with pool_reset)");
     c->launches = g.launches - c->launches_at_begin;
     cudaError_t e = cudaStreamEndCapture(g.stream, &c->graph);
@@ -254,6 +301,19 @@ uint64_t thvm_cuda_graph_input_bytes(int graph, int input) {
     Capture *c = graph_of(graph, "graph_input_bytes");
     if (!c || input < 0 || (size_t)input >= c->inputs.size()) return 0;
     return c->inputs[input].bytes;
+}
+
+// memory plan of a captured step: bytes of its arena, highest offset the plan reached, buffers placed in the arena, buffers
+// left to stream-ordered allocations inside the graph (arena full or absent), bytes requested over the whole step
+int thvm_cuda_graph_memory(int graph, uint64_t *arena_bytes, uint64_t *arena_used, uint32_t *arena_buffers, uint32_t *pool_buffers, uint64_t *bytes_requested) {
+    Capture *c = graph_of(graph, "graph_memory");
+    if (!c) return 1;
+    if (arena_bytes) *arena_bytes = c->arena_bytes;
+    if (arena_used) *arena_used = c->arena_high;
+    if (arena_buffers) *arena_buffers = c->arena_allocs;
+    if (pool_buffers) *pool_buffers = c->pool_allocs;
+    if (bytes_requested) *bytes_requested = c->arena_served;
+    return 0;
 }
 
 int thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels) {

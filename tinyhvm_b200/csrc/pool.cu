@@ -87,7 +87,8 @@ Buf &buf_checked(uint32_t id, const char *who) {
         if (outlives_capture) { settle_outside_capture(b, true); return b; }
         uint64_t sz = (b.bytes + 15) & ~15ull;
         if (sz == 0) sz = 16;
-        THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
+        if (g.cap && (b.ptr = capture_arena_alloc(sz)) != nullptr) b.in_arena = true;     // (a step constant inside a captured step)
+        else THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
         if (b.shadow && b.shadow_valid && b.bytes) {
             uint8_t *stage = ring_take(sz);
             memset(stage, 0, sz);
@@ -246,6 +247,7 @@ int thvm_cuda_init(void) {
     g.count = 1; g.persistent = 0;
     g.scratch = nullptr; g.scratch_bytes = 0;
     g.launches = 0; g.last_plan = ""; g.last_error.clear();
+    g.cur_bytes = g.peak_bytes = g.last_step_peak = 0;
     g.profile = getenv("THVM_PROFILE") != nullptr;
     g.profile_level = g.profile ? atoi(getenv("THVM_PROFILE")) : 0;
     g.ready = true;
@@ -258,8 +260,10 @@ static void release(uint32_t id) {
     if (b.ptr && g.cap && id < capture_first_id())
         capture_fail("the captured step frees a buffer that was allocated before the capture began");
     if (b.ptr) {
-        if (b.plain_alloc) THC_CUDA_OK(cudaFree(b.ptr));
+        if (b.in_arena) { if (g.cap) capture_arena_give_back(b.ptr, ((b.bytes + 15) & ~15ull) ? ((b.bytes + 15) & ~15ull) : 16); }
+        else if (b.plain_alloc) THC_CUDA_OK(cudaFree(b.ptr));
         else THC_CUDA_OK(cudaFreeAsync(b.ptr, g.stream));
+        if (!g.cap && !b.in_arena && b.bytes > SHADOW_MAX) { const uint64_t sz = (b.bytes + 15) & ~15ull; g.cur_bytes = g.cur_bytes > sz ? g.cur_bytes - sz : 0; }
     }
     free(b.shadow);
     b = Buf();
@@ -293,18 +297,23 @@ uint32_t thvm_cuda_buf_alloc(uint64_t bytes) {
     if (!g.ready) fatal("buf_alloc: backend not initialised (no CUDA device?)");
     if (g.count >= THC_MAX_BUFS) { set_error("buf_alloc: id space exhausted (%u)", THC_MAX_BUFS); return 0; }
     void *p = nullptr;
+    bool in_arena = false;
     if (bytes > SHADOW_MAX) {
         uint64_t sz = (bytes + 15) & ~15ull;
-        cudaError_t e = cudaMallocAsync(&p, sz, g.stream);
-        if (e != cudaSuccess) {
-            cudaGetLastError();
-            set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
-            return 0;
+        if (g.cap && (p = capture_arena_alloc(sz)) != nullptr) in_arena = true;     // planned: no allocator call in the recorded step
+        else {
+            cudaError_t e = cudaMallocAsync(&p, sz, g.stream);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                set_error("buf_alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+                return 0;
+            }
         }
+        if (!g.cap) { g.cur_bytes += sz; if (g.cur_bytes > g.peak_bytes) g.peak_bytes = g.cur_bytes; }
     }
     uint32_t id = g.count++;
     Buf &b = g.bufs[id];
-    b.live = true; b.ptr = p; b.bytes = bytes; b.refcount = 1;
+    b.live = true; b.ptr = p; b.bytes = bytes; b.refcount = 1; b.in_arena = in_arena;
     b.zero_pending = p != nullptr;                 // the zero-fill is issued on first use, and dropped if that use overwrites everything
     if (bytes <= SHADOW_MAX) {
         b.shadow = (uint8_t *)calloc(1, SHADOW_MAX);
@@ -432,6 +441,10 @@ void thvm_cuda_pool_reset(uint32_t keep) {
     if (first < 1) first = 1;
     for (uint32_t i = first; i < g.count; i++) if (g.bufs[i].live) release(i);
     if (first < g.count) g.count = first;
+    if (!g.cap) {                                  // a step ended: remember how much it held at its peak above what stays
+        g.last_step_peak = g.peak_bytes > g.cur_bytes ? g.peak_bytes - g.cur_bytes : 0;
+        g.peak_bytes = g.cur_bytes;
+    }
 }
 
 void thvm_cuda_pool_set_persistent(uint32_t max_buf) { g.persistent = max_buf; }

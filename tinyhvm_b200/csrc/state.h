@@ -23,6 +23,7 @@ struct Buf {
     bool     zero_pending = false; // fresh device memory whose zero-fill has not been issued yet
     bool     copy_pending = false; // an asynchronous read-back of this buffer may still be in flight on the copy stream
     bool     plain_alloc = false;  // ptr came from cudaMalloc (attached while a step was being captured), not from the stream-ordered pool
+    bool     in_arena = false;     // ptr lies in the step arena of the capture that is running (capture.cu): nothing to free
 };
 
 struct Capture;                    // capture.cu: the step being recorded as a CUDA graph
@@ -51,6 +52,9 @@ struct State {
     // library-owned scratch (two-pass reductions, operand splits); grow-only
     void        *scratch = nullptr;
     uint64_t     scratch_bytes = 0;
+    // device bytes behind live buffers: now, highest since the last pool_reset, and that peak of the last finished step
+    // above what stayed live (sizes the step arena of a capture)
+    uint64_t     cur_bytes = 0, peak_bytes = 0, last_step_peak = 0;
     // bookkeeping
     uint64_t     launches = 0;
     const char  *last_plan = "";
@@ -106,6 +110,10 @@ bool capturing();
 // mark the running capture unusable (capture_end will then fail with this reason); no-op outside a capture
 void capture_fail(const char *why);
 uint32_t capture_first_id();                                    // first buffer id handed out inside the capture
+// the step planner: memory for a buffer allocated inside a capture, from the capture's arena (null: arena full or absent);
+// give_back returns a block when the captured step frees the buffer
+void *capture_arena_alloc(uint64_t bytes);
+void capture_arena_give_back(void *ptr, uint64_t bytes);
 bool capture_write_is_input(uint64_t bytes);                    // a host write of this size made inside a capture is per-step data, not a constant
 uint8_t *capture_arena_take(uint64_t bytes);                    // pinned host memory that lives as long as the graph
 int  capture_add_input(void *dst, const void *src, uint64_t bytes);
