@@ -281,6 +281,11 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
         # ---- timed loop: launches back to back, the loss of step k read while step k + 1 runs
         ring = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(4)]
         done = [torch.cuda.Event() for _ in range(4)]
+        for k in range(3):                                 # the loop body itself, untimed: first use of the read-back ring
+            graph.launch(ext(k))
+            graph.results_async({"loss": ring[k % 4].numpy()})
+            done[k % 4].record(stream)
+        done[2].synchronize()
         if world > 1:
             dist.barrier()
         be.sync(); torch.cuda.synchronize()
@@ -332,6 +337,55 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
             "mode": ("cuda graph launch per step" if use_graph else "eager replay") + (", fused optimizer tail" if fused else ""),
             "split": split, "loss_first": losses[0], "loss_last": losses[-1],
             "error": be.last_error()}
+
+
+def hbm_peak():
+    """(GB/s, where it came from): the measured copy bandwidth of this pool's B200s, else the stated fallback."""
+    pk = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(pk.read_text()) if pk.exists() else {}
+    if "hbm_gbs" in peaks:
+        return float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6650 GB/s"
+
+
+# ------------------------------------------------------------------ config 5's layout copies: padding and window-to-plane
+def layout_section(be, stream, B: int, hbm_peak, iters: int = 10):
+    """The two layout-changing copies of the VGG-style step at its first block's size: the padding of a [B,64,64,64]
+    activation to 66x66 planes, materialised as ADD(pad(x), 0) (src/tensor/view/pad.c:2-16), and the pool gradient's
+    permute from window layout [B,64,32,32,2,2] back to planes.  Algorithmic bytes = input + output, each once."""
+    import torch
+    from tinyhvm_b200 import abi, synth
+    from tinyhvm_b200.abi import ADD, Dispatch, Leaf
+    seed = synth.SEED_BASE + 7
+    x = synth.normal(seed, 0, B * 64 * 64 * 64)
+    zero = Leaf(np.zeros(1, np.float32), abi.view_contiguous([1] * 6))
+    zero4 = Leaf(np.zeros(1, np.float32), abi.view_contiguous([1] * 4))
+    vpad = abi.view_pad(abi.view_contiguous([B, 64, 64, 64]), [0, 0, 1, 1], [0, 0, 1, 1])
+    vwin = abi.view_permute(abi.view_contiguous([B, 64, 32, 32, 2, 2]), [0, 1, 2, 4, 3, 5])
+    ds = {"pad_64x64_to_66x66": (Dispatch([Leaf(x, vpad), zero4], [(ADD, 0, 1)], [B, 64, 66, 66]), B * 64 * (64 * 64 + 66 * 66) * 4),
+          "window_to_plane_32x32x2x2": (Dispatch([Leaf(x, vwin), zero], [(ADD, 0, 1)], [B, 64, 32, 2, 32, 2]), 2 * B * 64 * 64 * 64 * 4)}
+    xid, zid = be.upload(x), be.upload(np.zeros(1, np.float32))
+    res = {}
+    for name, (d, nbytes) in ds.items():
+        out = be.alloc(d.out_numel * 4)
+        for _ in range(3):
+            be.dispatch_ids(out, [xid, zid], d)
+        be.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            be.dispatch_ids(out, [xid, zid], d)
+        e1.record(stream)
+        be.sync(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        got = be.read(out, np.float32, d.out_numel)
+        want = (np.pad(x.reshape(B, 64, 64, 64), ((0, 0), (0, 0), (1, 1), (1, 1))) if name.startswith("pad")
+                else x.reshape(B, 64, 32, 32, 2, 2).transpose(0, 1, 2, 4, 3, 5)).ravel()
+        res[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm_peak, "algorithmic_bytes": nbytes,
+                     "plan": be.last_plan(), "bit_exact": bool(np.array_equal(got, want))}
+    res["error"] = be.last_error()
+    be.reset(xid - 1)
+    return res
 
 
 # ------------------------------------------------------------------ clocks
@@ -481,7 +535,7 @@ def main():
     ap.add_argument("--unfused", action="store_true", help="lenet / vgg workloads: optimizer tail as recorded (all-reduce call + one dispatch and copy per parameter tensor)")
     ap.add_argument("--no-sustain", action="store_true", help="skip the ~0.6 s untimed continuation used for clock sampling (profiling runs)")
     ap.add_argument("--no-extras", action="store_true", help="skip the LeNet / VGG / GEMM extras (profiling the headline kernels alone)")
-    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "lenet", "vgg", "lenet_live", "cpu_baselines"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "gemm", "conv", "layout", "lenet", "vgg", "lenet_live", "cpu_baselines"],
                     help="chain = the headline config; gemm = only the three config-3 GEMMs; lenet / vgg = only the config-4 / config-5 training steps")
     ap.add_argument("--gemm-size", type=int, default=4096)
     args = ap.parse_args()
@@ -532,6 +586,16 @@ def main():
             print(json.dumps({"metric": "conv_3xtf32_tflops", "unit": "TFLOP/s", "n_gpus": world, "dtype": "f32 (3xTF32 on tcgen05)",
                               "config": {"workload": f"cfg5 conv 64->64 3x3 at 64x64, batch {args.conv_batch}: forward and weight gradient"},
                               "convs": r, "value": min(v["tflops"] for v in r.values() if isinstance(v, dict))}))
+        be.shutdown()
+        return
+    if args.workload == "layout":
+        peak = hbm_peak()[0]
+        r = layout_section(be, stream, args.conv_batch, peak)
+        if rank == 0:
+            print(json.dumps({"metric": "layout_copy_hbm_gbs", "unit": "GB/s", "n_gpus": world, "dtype": "f32",
+                              "config": {"workload": f"cfg5 layout copies at batch {args.conv_batch}: padding 64x64 -> 66x66, window layout -> planes",
+                                         "l2": f"input {args.conv_batch * 64 * 64 * 64 * 4 >> 20} MiB per launch"},
+                              "copies": r, "value": min(v["gbs"] for v in r.values() if isinstance(v, dict))}))
         be.shutdown()
         return
     if args.workload in CNN:
@@ -678,18 +742,13 @@ def main():
     lenet = vgg = None
     if rows == ROWS and not args.no_extras:                # every rank takes part (gradient all-reduce at N > 1)
         try:
-            lenet = cnn_section(be, stream, rank, world, "lenet")
+            lenet = cnn_section(be, stream, rank, world, "lenet", steps=40)
             vgg = cnn_section(be, stream, rank, world, "vgg", steps=5)
         except Exception as ex:                            # an extra: never lose the headline line over it
             lenet = lenet or {"error": repr(ex)}
             vgg = vgg or {"error": repr(ex)}
     if rank == 0:
-        peaks = {}
-        pk = ROOT / "MEASURED_PEAKS.json"
-        if pk.exists():
-            peaks = json.loads(pk.read_text())
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        peak, peak_src = hbm_peak()
         dom = ("chain_bwd", plan_bwd, bwd_bytes, bwd_ms) if bwd_ms >= fwd_ms else ("chain_fwd", plan_fwd, fwd_bytes, fwd_ms)
         oth = ("chain_fwd", plan_fwd, fwd_bytes, fwd_ms) if bwd_ms >= fwd_ms else ("chain_bwd", plan_bwd, bwd_bytes, bwd_ms)
 

@@ -235,6 +235,10 @@ def contraction_cases():
         # thin shapes on the CUDA-core kernels: many rows x few columns, and few outputs x very long K
         cases.conv_fprop_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 5000, 40, 12), cases.mm_case(rng, 4100, 300, 27),
         cases.conv_wgrad_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 10, 6000, 20), cases.mm_case(rng, 16, 9000, 150, ta=True),
+        # a 3-channel first layer: K = 27 with 64 (four columns per load) and 50 output channels on the row kernel, its
+        # weight gradient (27 x 64 outputs, long K) on the tiled slice kernel; 40 x 100 outputs do not tile: plain slice kernel
+        cases.conv_fprop_case(rng, 2, 3, 50, 50, 64, 3), cases.conv_fprop_case(rng, 2, 3, 50, 50, 50, 3),
+        cases.conv_wgrad_case(rng, 4, 3, 34, 34, 64, 3), cases.mm_case(rng, 40, 5000, 100),
     ]
 
 
@@ -249,7 +253,7 @@ def test_contraction_kernel(cuda, oracle):
         check(d, got, oracle.run(d), oracle=oracle)
     print("plans:", plans)
     assert all(p.startswith("gemm") or p.startswith("contract_skinny") for p in plans), plans
-    assert sum(p == "contract_skinny_rows" for p in plans) >= 3, plans
+    assert sum(p == "contract_skinny_rows" for p in plans) >= 5, plans
     assert any("splitk" in p for p in plans), plans
     assert sum(p.startswith("gemm_pair") or p.startswith("gemm_tma") for p in plans) >= 6, plans
     assert sum(p.startswith("gemm_tma") for p in plans) >= 4, plans
@@ -281,4 +285,27 @@ def test_read_back_variants(cuda):
     assert np.array_equal(out_a, big)
     assert np.array_equal(cuda.read(dst, np.float32, big.size), np.zeros_like(big))
     cuda.reset(0)
+    assert cuda.last_error() == ""
+
+
+def test_layout_copy_kernels(cuda, oracle):
+    """Padding materialised as ADD(pad(x), 0) (src/tensor/view/pad.c:2-16: a mask and a negative offset, never a copy)
+    and the pool gradient's window-to-plane permute run on their own bandwidth kernels when the planes are contiguous;
+    shapes those kernels decline (odd extents, permuted planes) fall to the general forms.  Bit for bit either way."""
+    rng = np.random.default_rng(31)
+    eligible = [(cases.pad_case(rng, 3, 5, 16, 16, 1), "pad_planes"), (cases.pad_case(rng, 2, 1, 28, 28, 2), "pad_planes"),
+                (cases.pad_case(rng, 4, 64, 64, 64, 1), "pad_planes"), (cases.pad_case(rng, 1, 7, 9, 30, 1), "pad_planes"),
+                (cases.permute_copy_case(rng, [2, 3, 4, 6, 2, 2], [0, 1, 2, 4, 3, 5]), "window_to_plane"),
+                (cases.permute_copy_case(rng, [4, 64, 32, 32, 2, 2], [0, 1, 2, 4, 3, 5]), "window_to_plane"),
+                (cases.permute_copy_case(rng, [5, 8, 2, 2], [0, 2, 1, 3]), "window_to_plane")]
+    declined = [cases.pad_case(rng, 2, 3, 5, 7, 2), cases.permute_copy_case(rng, [2, 3, 4, 5, 2, 2], [0, 1, 2, 4, 3, 5]),
+                cases.permute_copy_case(rng, [2, 3, 4, 6, 2, 2], [1, 0, 2, 4, 3, 5])]
+    for d, plan in eligible:
+        got = cuda.run(d)
+        assert cuda.last_plan() == plan, (d.name, cuda.last_plan())
+        assert same(got, oracle.run(d)), d.name
+    for d in declined:
+        got = cuda.run(d)
+        assert cuda.last_plan() not in ("pad_planes", "window_to_plane"), (d.name, cuda.last_plan())
+        assert same(got, oracle.run(d)), d.name
     assert cuda.last_error() == ""

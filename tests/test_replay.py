@@ -256,6 +256,13 @@ def test_captured_step_graph_matches_recorded_run(tmp_path, cuda):
     launches_eager = cuda.launches()
     step = rp.capture(rp.cycles[1], ext(2))
     assert cuda.launches() - launches_eager == step.n_kernels > 0
+    # the step's memory plan: every buffer the step allocates sits at a fixed offset of one arena made when the capture
+    # began (sized from the eager step before it), so the recorded graph holds no allocation or free nodes
+    ab, au, bt = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    na, npool = C.c_uint32(), C.c_uint32()
+    assert cuda.lib.thvm_cuda_graph_memory(step.handle, C.byref(ab), C.byref(au), C.byref(na), C.byref(npool), C.byref(bt)) == 0
+    assert na.value > 20 and npool.value == 0, (na.value, npool.value)
+    assert 0 < au.value <= ab.value and au.value <= bt.value + 1024 * na.value, (au.value, ab.value, bt.value)
     for s in range(2, steps):
         step.launch(ext(s))
         losses.append(float(step.results()["loss"][0]))

@@ -10,14 +10,17 @@
 // its CPU backend evaluates one product at a time (src/backend/cpu/dispatch.c:169-218).
 //
 // Kernels in this translation unit, chosen per plan by the recogniser (gemm_host.inc):
-//   k_gemm_pair_tma      (gemm_tma.inc) CTA pair, 256-row tiles, operand k-blocks by TMA tile loads: matrices whose
-//                        operands are (or are transposed into) k-contiguous form, NCHW convolutions over
-//                        channels-last re-laid operands;
-//   k_gemm_pair_3xtf32   CTA pair, operands gathered with cp.async through separable offsets (implicit im2col:
-//                        weight gradients, operands with odd pitches, K not a multiple of 4);
+//   k_gemm_ps            (gemm_ps.inc) persistent single-CTA kernel for outputs of at most 128 columns: one CTA per SM
+//                        walks 128-row tiles; A tiles, B tiles and tensor-memory stages are three rings; the A operand
+//                        goes to tensor memory (hi and lo split in registers), accumulators are double-buffered so
+//                        the epilogue of one tile overlaps the next tile's MMAs;
+//   k_gemm_pair_ta       (gemm_ta.inc) CTA pair, 256-row tiles, A operand in tensor memory, B by tile loads: wider
+//                        outputs (the 4096^3 matrices, 256-channel convolutions);
+//   k_gemm_pair_3xtf32   CTA pair, operands gathered with cp.async through separable offsets (implicit im2col for what
+//                        the tile-load forms do not cover: 3 input channels, odd pitches, K not a multiple of 4);
 //   k_gemm_3xtf32        single CTA, 128x128 tile, same gather, for outputs with fewer than 256 rows;
 //   k_skinny_rows / _k   (gemm_skinny.inc) CUDA-core kernels for shapes too thin for a tensor-core tile.
-// Common structure of the tensor-core kernels: sixteen producer warps put 128x32 k-blocks of A and B into
+// The two gather kernels below share this structure: sixteen producer warps put 128x32 k-blocks of A and B into
 // shared memory in the K-major 128-byte-swizzled layout the MMA reads.  The raw f32 tile is the high part
 // as it stands (the tf32 MMA ignores the low 13 mantissa bits); a pass over the tile writes the low parts.
 // One elected lane of the MMA warp issues, per k-block, 4 k-steps x 3 products and hands the stage back

@@ -156,6 +156,27 @@ static bool build_desc(Plan *p, const thc_view_t **views, const thc_tracker_t *c
     return true;
 }
 
+// What profile_report divides the measured time into: the Metal backend estimates out_numel * reduce_numel * n_ops
+// operations and (n_leaves * iteration points + outputs) * 4 bytes (src/backend/metal/codegen.m:1023-1031); here the
+// bytes are the algorithmic ones, each leaf counted over the dims it actually walks, in its own dtype.
+static void estimate(Plan *p) {
+    const GenDesc &D = p->host;
+    p->est_ops = D.full_numel * (unsigned long long)((D.n_ops ? D.n_ops : 1) + (D.has_reduce ? 1 : 0));
+    p->est_out_bytes = (D.has_reduce ? D.out_numel : D.full_numel) * dtype_bytes(D.out_dtype);
+    for (uint32_t i = 0; i < D.n_leaves; i++) {
+        const DLeaf &L = D.leaves[i];
+        unsigned long long n = 1;
+        if (L.tracker >= 0) n = D.full_numel;       // stacked views: no cheap bound, count every point
+        else for (uint32_t d = 0; d < D.rank && d < L.v.rank; d++) {
+            if (L.v.strides[d] == 0 || L.v.dims[d] <= 1) continue;
+            uint32_t ext = L.v.dims[d] < D.full_dims[d] ? L.v.dims[d] : D.full_dims[d];
+            if (L.v.has_mask && L.v.me[d] > L.v.mb[d] && L.v.me[d] - L.v.mb[d] < ext) ext = L.v.me[d] - L.v.mb[d];
+            n *= ext;
+        }
+        p->est_leaf_bytes[i] = n * dtype_bytes(L.dtype);
+    }
+}
+
 // The device copy of the descriptor, made the first time the generic kernel runs the plan.  Memory allocated while a
 // step is being recorded would belong to the recorded graph, so inside a capture this refuses instead (false).
 static bool ensure_dev_desc(Plan *p) {
@@ -224,6 +245,7 @@ void thvm_cuda_dispatch_kernel_rs(uint32_t out_buf, uint32_t *leaf_bufs, const t
         }
         p->kind = PLAN_GENERIC;
         if (!g.force_generic) classify_plan(p);
+        estimate(p);
         (*cache)[key] = p;
     }
 
@@ -232,7 +254,9 @@ void thvm_cuda_dispatch_kernel_rs(uint32_t out_buf, uint32_t *leaf_bufs, const t
         Buf &lb = buf_checked(leaf_bufs[i], "dispatch(leaf)");
         args.leaf[i] = lb.ptr;
         args.cap[i] = lb.bytes / dtype_bytes(p->host.leaves[i].dtype);
+        if (g.profile) g.prof_bytes = (i ? g.prof_bytes : p->est_out_bytes) + (p->est_leaf_bytes[i] < lb.bytes ? p->est_leaf_bytes[i] : lb.bytes);
     }
+    if (g.profile) g.prof_ops = p->est_ops;
     uint64_t need_out = p->host.has_reduce ? p->host.out_numel : p->host.full_numel;
     Buf &ob = buf_for_output(out_buf, "dispatch(out)", need_out * dtype_bytes(p->host.out_dtype));   // after the leaves: out may alias one
     args.out = ob.ptr;

@@ -29,6 +29,10 @@ struct Plan {
     unsigned long long pool_planes = 0; // PLAN_POOL: contiguous [planes, pool_h, pool_w] input starting at element pool_off
     uint32_t   pool_h = 0, pool_w = 0;
     long long  pool_off = 0, pool_g_off = 0, pool_m_off = 0, pool_one_off = 0;
+    // estimates for profile_report: op evaluations (reduce accumulation counted as one op) and algorithmic bytes
+    // (every leaf element addressed once: dims walked with stride 0 do not count, and a leaf never counts for more than
+    // its buffer holds, which is what overlapping convolution windows come to; plus the output)
+    unsigned long long est_ops = 0, est_out_bytes = 0, est_leaf_bytes[THC_MAX_LEAVES] = {};
 };
 
 // Decide the family for a freshly built plan (sets kind / fast).

@@ -131,7 +131,7 @@ void *scratch_reserve(uint64_t bytes) {
 }
 
 // ---- per-family launch statistics (profile_report) ----
-struct PlanStat { uint64_t launches = 0; double ms = 0; };
+struct PlanStat { uint64_t launches = 0; double ms = 0; unsigned long long ops = 0, bytes = 0; };
 static std::map<std::string, PlanStat> *plan_stats = nullptr;
 static cudaEvent_t prof_ev[2] = {nullptr, nullptr};
 static bool prof_open = false;
@@ -145,12 +145,20 @@ void after_launch(const char *plan) {
         if (!plan_stats) plan_stats = new std::map<std::string, PlanStat>();
         PlanStat &s = (*plan_stats)[plan];
         s.launches++;
+        // the estimates of a dispatch go to its first launch that is not an operand pre-pass of a contraction
+        static const char *const prepass[] = {"conv_relayout_input", "conv_relayout_weights", "gemm_transpose_operand", "wgrad_pad_width"};
+        bool pre = false;
+        for (const char *q : prepass) pre = pre || strcmp(plan, q) == 0;
+        const unsigned long long ops = pre ? 0 : g.prof_ops, bytes = pre ? 0 : g.prof_bytes;
+        s.ops += ops; s.bytes += bytes;
+        if (!pre) g.prof_ops = g.prof_bytes = 0;
         if (prof_open) {           // close the bracket opened by profile_begin
             THC_CUDA_OK(cudaEventRecord(prof_ev[1], g.stream));
             THC_CUDA_OK(cudaEventSynchronize(prof_ev[1]));
             float ms = 0; THC_CUDA_OK(cudaEventElapsedTime(&ms, prof_ev[0], prof_ev[1]));
             s.ms += ms; prof_open = false;
-            if (g.profile_level >= 2 && (ms > 0.1f || g.profile_level >= 3)) fprintf(stderr, "thvm_cuda slow launch: %-22s %8.3f ms  %s\n", plan, ms, g.last_shape);
+            if (g.profile_level >= 2 && (ms > 0.1f || g.profile_level >= 3))
+                fprintf(stderr, "thvm_cuda slow launch: %-22s %8.3f ms (%9.2f GFLOPS %7.1f GB/s)  %s\n", plan, ms, ops / (ms * 1e6), bytes / (ms * 1e6), g.last_shape);
         }
     }
 }
@@ -454,10 +462,15 @@ void thvm_cuda_end_batch(void) {}   // one stream already orders and batches the
 
 void thvm_cuda_profile_report(void) {
     if (!plan_stats) { fprintf(stderr, "thvm_cuda profile: no launches recorded (set THVM_PROFILE=1 before init)\n"); return; }
-    fprintf(stderr, "thvm_cuda profile: %-22s %10s %12s\n", "kernel family", "launches", "gpu ms");
-    for (auto &kv : *plan_stats)
-        fprintf(stderr, "thvm_cuda profile: %-22s %10llu %12.3f\n", kv.first.c_str(),
-                (unsigned long long)kv.second.launches, kv.second.ms);
+    // per family: launches, device time, and the estimated operations / algorithmic bytes of its dispatches with the
+    // rates they come to (the figures the Metal backend prints per kernel, src/backend/metal/profile_kernel.m:45-62)
+    fprintf(stderr, "thvm_cuda profile: %-22s %10s %12s %12s %10s %12s %10s\n", "kernel family", "launches", "gpu ms", "Gop", "GFLOPS", "GB", "GB/s");
+    for (auto &kv : *plan_stats) {
+        const PlanStat &s = kv.second;
+        const double per_sec = s.ms > 0 ? 1e3 / s.ms : 0.0;     // families that are never timed on their own report no rate
+        fprintf(stderr, "thvm_cuda profile: %-22s %10llu %12.3f %12.3f %10.1f %12.3f %10.1f\n", kv.first.c_str(),
+                (unsigned long long)s.launches, s.ms, s.ops * 1e-9, s.ops * 1e-9 * per_sec, s.bytes * 1e-9, s.bytes * 1e-9 * per_sec);
+    }
 }
 void thvm_cuda_profile_reset(void) { if (plan_stats) plan_stats->clear(); g.launches = 0; }
 

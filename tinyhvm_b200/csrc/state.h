@@ -62,6 +62,7 @@ struct State {
     std::string  last_error;
     // profiling (THVM_PROFILE / profile_report)
     bool         profile = false;
+    unsigned long long prof_ops = 0, prof_bytes = 0;   // estimates of the dispatch about to launch (profile_report)
     int          profile_level = 0;   // THVM_PROFILE=2: also print every launch slower than 0.1 ms with its shape; 3: every launch
     char         last_shape[160] = {0};
 };
