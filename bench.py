@@ -267,6 +267,9 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
         be.lib.thvm_cuda_graph_memory(graph.handle, C.byref(ab), C.byref(au), C.byref(na), C.byref(npool), C.byref(bt))
         split["memory_plan"] = {"arena_bytes": ab.value, "arena_bytes_used": au.value, "buffers_in_arena": na.value,
                                 "buffers_left_to_allocator": npool.value, "bytes_requested_per_step": bt.value}
+        nk, ncp, nms, no = (C.c_uint32() for _ in range(4))
+        be.lib.thvm_cuda_graph_nodes(graph.handle, C.byref(nk), C.byref(ncp), C.byref(nms), C.byref(no))
+        split["graph_nodes"] = {"kernels": nk.value, "copies": ncp.value, "memsets": nms.value, "others": no.value}
         # ---- where a step's time goes: device time of one graph launch (events around it, host waits each time)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         dev_ms = []

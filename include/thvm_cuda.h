@@ -285,6 +285,9 @@ int      thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes
  * valid once the stream has passed it (record an event on thvm_cuda_stream() after the call, or thvm_cuda_sync). */
 int      thvm_cuda_graph_result_async(int graph, int result, void *out, uint64_t bytes);
 int      thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, uint64_t *n_kernels);
+/* Node census of the recorded graph: kernel nodes, copy nodes (inputs, staged constants, read-backs), memset nodes
+ * (zero-fills), everything else (allocation / free nodes, empty nodes).  0 = ok. */
+int      thvm_cuda_graph_nodes(int graph, uint32_t *kernels, uint32_t *copies, uint32_t *memsets, uint32_t *others);
 /* For hosts that upload their per-step data with plain buf_write inside the step (the reference's drivers make a fresh
  * tensor per batch): the byte sizes of those uploads, declared before capture_begin.  While capturing, a buf_write of
  * exactly one of these sizes is an input, in call order; every other staged write stays a constant of the step (n = 0

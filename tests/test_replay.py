@@ -263,6 +263,9 @@ def test_captured_step_graph_matches_recorded_run(tmp_path, cuda):
     assert cuda.lib.thvm_cuda_graph_memory(step.handle, C.byref(ab), C.byref(au), C.byref(na), C.byref(npool), C.byref(bt)) == 0
     assert na.value > 20 and npool.value == 0, (na.value, npool.value)
     assert 0 < au.value <= ab.value and au.value <= bt.value + 1024 * na.value, (au.value, ab.value, bt.value)
+    nk, ncp, nms, no = (C.c_uint32() for _ in range(4))
+    assert cuda.lib.thvm_cuda_graph_nodes(step.handle, C.byref(nk), C.byref(ncp), C.byref(nms), C.byref(no)) == 0
+    assert nk.value == step.n_kernels and ncp.value >= 3 and no.value == 0, (nk.value, ncp.value, nms.value, no.value)
     for s in range(2, steps):
         step.launch(ext(s))
         losses.append(float(step.results()["loss"][0]))

@@ -85,6 +85,7 @@ SYMBOLS = {
     "thvm_cuda_graph_result": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),
     "thvm_cuda_graph_result_async": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),
     "thvm_cuda_graph_counts": (C.c_int, [C.c_int, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u64)]),
+    "thvm_cuda_graph_nodes": (C.c_int, [C.c_int, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "thvm_cuda_graph_destroy": (None, [C.c_int]),
     "thvm_cuda_graph_memory": (C.c_int, [C.c_int, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u64)]),
     "thvm_cuda_capture_input_sizes": (None, [C.POINTER(_u64), _u32]),

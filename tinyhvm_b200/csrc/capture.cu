@@ -44,6 +44,13 @@ struct Capture {
     uint64_t arena_bytes = 0, arena_high = 0, arena_served = 0;       // size, highest offset used, bytes handed out in total
     uint32_t arena_allocs = 0, pool_allocs = 0;                        // buffers placed in the arena / left to the pool (arena full)
     std::vector<std::pair<uint64_t, uint64_t>> free_list;              // (offset, bytes), sorted by offset
+    // Step constants: what the host writes inside the step (scalars, small tables) is the same at every replay.  Instead of
+    // one copy node each in the recorded chain, they sit in the top CONST_REGION bytes of the arena, which the free list
+    // never sees, and are uploaded once while the step is recorded.  One that the step itself overwrites later (`dirty`)
+    // gets a copy node at the end of the graph that puts its bytes back for the next replay.
+    struct Const { uint8_t *dev; uint8_t *src; uint64_t bytes; bool dirty; };
+    std::vector<Const> consts;
+    uint64_t const_pos = 0, const_end = 0;                             // bump range inside the arena
     // host-side state of every buffer that existed when the capture began, put back if the capture is refused
     struct Snap { uint32_t id; void *ptr; uint32_t refcount; bool shadow_valid, zero_pending, plain_alloc; uint8_t shadow[256]; };
     std::vector<Snap> snaps;
@@ -55,6 +62,7 @@ static std::vector<Capture *> graphs;              // handle = index + 1
 static uint64_t input_sizes[8];                    // capture: host writes of exactly these sizes count as inputs (beside writes above 1 MiB)
 static uint32_t n_input_sizes = 0;
 constexpr uint64_t ARENA_CHUNK = 4ull << 20;
+constexpr uint64_t CONST_REGION = 16ull << 20;
 
 bool capturing() { return g.cap != nullptr; }
 
@@ -96,6 +104,27 @@ void capture_arena_give_back(void *ptr, uint64_t bytes) {
         c.free_list[i - 1].second += c.free_list[i].second; c.free_list.erase(c.free_list.begin() + (long)i);
     }
 }
+void *capture_const_place(const void *host, uint64_t host_bytes, uint64_t buf_bytes) {
+    if (!g.cap || !g.cap->arena) return nullptr;
+    Capture &c = *g.cap;
+    const uint64_t need = (buf_bytes + 255) & ~255ull;
+    if (host_bytes > buf_bytes || c.const_pos + need > c.const_end) return nullptr;
+    uint8_t *dev = c.arena + c.const_pos;
+    c.const_pos += need;
+    uint8_t *src = capture_arena_take(need);           // pinned, lives as long as the graph: the upload below and a put-back node read it
+    memset(src, 0, need);
+    memcpy(src, host, host_bytes);
+    THC_CUDA_OK(cudaMemcpyAsync(dev, src, need, cudaMemcpyHostToDevice, g.copy_stream));   // really runs: the copy stream is not recording
+    c.consts.push_back({dev, src, need, false});
+    c.arena_served += need; c.arena_allocs++;
+    return dev;
+}
+
+void capture_const_dirty(void *dev) {
+    if (!g.cap) return;
+    for (Capture::Const &k : g.cap->consts) if (k.dev == dev) { k.dirty = true; return; }
+}
+
 bool capture_write_is_input(uint64_t bytes) { for (uint32_t i = 0; i < n_input_sizes; i++) if (input_sizes[i] == bytes) return true; return false; }
 
 uint8_t *capture_arena_take(uint64_t bytes) {
@@ -189,9 +218,13 @@ int thvm_cuda_capture_begin(void) {
     }
     // the arena: what the last finished step held at its peak, plus room for the holes a first-fit replay leaves
     if (g.last_step_peak) {
-        c->arena_bytes = g.last_step_peak + g.last_step_peak / 4 + (64ull << 20);
+        c->arena_bytes = (g.last_step_peak + g.last_step_peak / 4 + (64ull << 20)) & ~255ull;     // (the constants' part starts at its end minus a multiple of 256)
         if (cudaMalloc((void **)&c->arena, c->arena_bytes) != cudaSuccess) { cudaGetLastError(); c->arena = nullptr; c->arena_bytes = 0; }
-        else c->free_list.push_back({0, c->arena_bytes});
+        else {
+            c->const_end = c->arena_bytes;
+            c->const_pos = c->arena_bytes > 4 * CONST_REGION ? c->arena_bytes - CONST_REGION : c->arena_bytes;
+            c->free_list.push_back({0, c->const_pos});
+        }
     }
     cudaError_t e = cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed);
     if (e != cudaSuccess) { cudaGetLastError(); set_error("capture_begin: %s", cudaGetErrorString(e)); destroy(c); return 1; }
@@ -214,8 +247,11 @@ int thvm_cuda_capture_end(void) {
         if (g.bufs[i].live && g.bufs[i].ptr && !g.bufs[i].plain_alloc)     // (a buffer in the step arena counts too: its memory is the graph's)
             capture_fail("a buffer allocated inside the captured step is still live: the step must free what it allocates (end with pool_reset)");
     c->launches = g.launches - c->launches_at_begin;
+    for (const Capture::Const &k : c->consts)          // constants the step overwrote: put back at the end of every replay
+        if (k.dirty) THC_CUDA_OK(cudaMemcpyAsync(k.dev, k.src, k.bytes, cudaMemcpyHostToDevice, g.stream));
     cudaError_t e = cudaStreamEndCapture(g.stream, &c->graph);
     g.cap = nullptr;
+    THC_CUDA_OK(cudaStreamSynchronize(g.copy_stream));     // the constants' uploads have landed before the first launch
     // buffers the step left behind point into memory of a graph that will never run: forget them
     // (no free call: the addresses belong to the graph) and rewind the ids, as if the step had not happened
     // The older buffers go back to the host-side state they had when the capture began: shadows, reference counts and
@@ -322,6 +358,29 @@ int thvm_cuda_graph_counts(int graph, uint32_t *n_inputs, uint32_t *n_results, u
     if (n_inputs) *n_inputs = (uint32_t)c->inputs.size();
     if (n_results) *n_results = (uint32_t)c->results.size();
     if (n_kernels) *n_kernels = c->launches;
+    return 0;
+}
+
+int thvm_cuda_graph_nodes(int graph, uint32_t *kernels, uint32_t *copies, uint32_t *memsets, uint32_t *others) {
+    Capture *c = graph_of(graph, "graph_nodes");
+    if (!c) return 1;
+    size_t n = 0;
+    if (cudaGraphGetNodes(c->graph, nullptr, &n) != cudaSuccess) { cudaGetLastError(); return 1; }
+    std::vector<cudaGraphNode_t> nodes(n);
+    if (n && cudaGraphGetNodes(c->graph, nodes.data(), &n) != cudaSuccess) { cudaGetLastError(); return 1; }
+    uint32_t k = 0, cp = 0, ms = 0, ot = 0;
+    for (size_t i = 0; i < n; i++) {
+        cudaGraphNodeType t;
+        if (cudaGraphNodeGetType(nodes[i], &t) != cudaSuccess) { cudaGetLastError(); return 1; }
+        if (t == cudaGraphNodeTypeKernel) k++;
+        else if (t == cudaGraphNodeTypeMemcpy) cp++;
+        else if (t == cudaGraphNodeTypeMemset) ms++;
+        else ot++;
+    }
+    if (kernels) *kernels = k;
+    if (copies) *copies = cp;
+    if (memsets) *memsets = ms;
+    if (others) *others = ot;
     return 0;
 }
 

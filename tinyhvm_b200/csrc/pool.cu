@@ -79,7 +79,8 @@ static void settle_outside_capture(Buf &b, bool attach) {
     b.zero_pending = false;
 }
 
-Buf &buf_checked(uint32_t id, const char *who) {
+// `will_overwrite`: the caller is about to overwrite the whole buffer, so memory that is attached here needs no contents.
+static Buf &buf_attach(uint32_t id, const char *who, bool will_overwrite) {
     Buf &b = buf_live(id, who);
     fence_copy(b);                                  // whatever comes next on the main stream stays behind a running read-back of b
     const bool outlives_capture = g.cap && id < capture_first_id();
@@ -87,15 +88,20 @@ Buf &buf_checked(uint32_t id, const char *who) {
         if (outlives_capture) { settle_outside_capture(b, true); return b; }
         uint64_t sz = (b.bytes + 15) & ~15ull;
         if (sz == 0) sz = 16;
-        if (g.cap && (b.ptr = capture_arena_alloc(sz)) != nullptr) b.in_arena = true;     // (a step constant inside a captured step)
-        else THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
-        if (b.shadow && b.shadow_valid && b.bytes) {
-            uint8_t *stage = ring_take(sz);
-            memset(stage, 0, sz);
-            memcpy(stage, b.shadow, b.bytes);
-            THC_CUDA_OK(cudaMemcpyAsync(b.ptr, stage, sz, cudaMemcpyHostToDevice, g.stream));
-        } else {
-            THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.stream));
+        const bool have_data = b.shadow && b.shadow_valid && b.bytes && !will_overwrite;
+        // inside a recorded step the host's bytes are a constant of the step: placed and uploaded once, no copy node
+        if (g.cap && have_data && (b.ptr = capture_const_place(b.shadow, b.bytes, sz)) != nullptr) { b.in_arena = true; b.step_const = true; }
+        else {
+            if (g.cap && (b.ptr = capture_arena_alloc(sz)) != nullptr) b.in_arena = true;
+            else THC_CUDA_OK(cudaMallocAsync(&b.ptr, sz, g.stream));
+            if (have_data) {
+                uint8_t *stage = ring_take(sz);
+                memset(stage, 0, sz);
+                memcpy(stage, b.shadow, b.bytes);
+                THC_CUDA_OK(cudaMemcpyAsync(b.ptr, stage, sz, cudaMemcpyHostToDevice, g.stream));
+            } else if (!will_overwrite) {
+                THC_CUDA_OK(cudaMemsetAsync(b.ptr, 0, sz, g.stream));
+            }
         }
     }
     if (b.zero_pending) {
@@ -105,6 +111,8 @@ Buf &buf_checked(uint32_t id, const char *who) {
     }
     return b;
 }
+
+Buf &buf_checked(uint32_t id, const char *who) { return buf_attach(id, who, false); }
 
 void fence_copy(Buf &b) {
     if (!b.copy_pending) return;
@@ -116,8 +124,11 @@ Buf &buf_for_output(uint32_t id, const char *who, uint64_t bytes_written) {
     Buf &b = buf_live(id, who);
     fence_copy(b);
     // (not for a buffer that outlives a running capture: the overwrite is only being recorded)
-    if (b.ptr && b.zero_pending && bytes_written >= b.bytes && !(g.cap && id < capture_first_id())) b.zero_pending = false;
-    return buf_checked(id, who);
+    const bool whole = bytes_written >= b.bytes && !(g.cap && id < capture_first_id());
+    if (b.ptr && b.zero_pending && whole) b.zero_pending = false;
+    Buf &r = buf_attach(id, who, whole);
+    if (r.step_const) capture_const_dirty(r.ptr);
+    return r;
 }
 
 void *scratch_reserve(uint64_t bytes) {
@@ -268,7 +279,7 @@ static void release(uint32_t id) {
     if (b.ptr && g.cap && id < capture_first_id())
         capture_fail("the captured step frees a buffer that was allocated before the capture began");
     if (b.ptr) {
-        if (b.in_arena) { if (g.cap) capture_arena_give_back(b.ptr, ((b.bytes + 15) & ~15ull) ? ((b.bytes + 15) & ~15ull) : 16); }
+        if (b.in_arena) { if (g.cap && !b.step_const) capture_arena_give_back(b.ptr, ((b.bytes + 15) & ~15ull) ? ((b.bytes + 15) & ~15ull) : 16); }
         else if (b.plain_alloc) THC_CUDA_OK(cudaFree(b.ptr));
         else THC_CUDA_OK(cudaFreeAsync(b.ptr, g.stream));
         if (!g.cap && !b.in_arena && b.bytes > SHADOW_MAX) { const uint64_t sz = (b.bytes + 15) & ~15ull; g.cur_bytes = g.cur_bytes > sz ? g.cur_bytes - sz : 0; }
@@ -367,6 +378,17 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
     }
     if (!b.ptr) return;                            // host-only buffer: uploaded if and when the device needs it
     fence_copy(b);
+    if (g.cap && b.in_arena && !b.step_const && b.zero_pending && bytes <= RING_MAX_MSG && !capture_write_is_input(bytes)) {
+        // a constant of the recorded step, written into a buffer nothing has read or written yet: move the buffer to the
+        // constants' part of the arena and upload it once (zero-padded), instead of a copy node in the chain
+        const uint64_t sz = ((b.bytes + 15) & ~15ull) ? ((b.bytes + 15) & ~15ull) : 16;
+        void *p = capture_const_place(data, bytes, sz);
+        if (p) {
+            capture_arena_give_back(b.ptr, sz);
+            b.ptr = p; b.step_const = true; b.zero_pending = false;
+            return;
+        }
+    }
     if (b.zero_pending) {
         if (g.cap && id < capture_first_id()) settle_outside_capture(b, false);
         else {
@@ -375,6 +397,7 @@ void thvm_cuda_buf_write(uint32_t id, const void *data, uint64_t bytes) {
         }
     }
     if (g.cap && capture_write_is_input(bytes)) { capture_add_input(b.ptr, data, bytes); return; }
+    if (b.step_const) capture_const_dirty(b.ptr);      // written again inside the step: the first bytes are put back at the end
     if (bytes <= RING_MAX_MSG) {
         uint8_t *stage = ring_take(bytes);
         memcpy(stage, data, bytes);

@@ -24,6 +24,7 @@ struct Buf {
     bool     copy_pending = false; // an asynchronous read-back of this buffer may still be in flight on the copy stream
     bool     plain_alloc = false;  // ptr came from cudaMalloc (attached while a step was being captured), not from the stream-ordered pool
     bool     in_arena = false;     // ptr lies in the step arena of the capture that is running (capture.cu): nothing to free
+    bool     step_const = false;   // in_arena, in the part that is never handed out twice: a constant of the recorded step, uploaded once
 };
 
 struct Capture;                    // capture.cu: the step being recorded as a CUDA graph
@@ -92,7 +93,8 @@ void *scratch_reserve(uint64_t bytes);
 // before `b` is overwritten or freed on the main stream: wait for a read-back of it that may still be running
 void fence_copy(Buf &b);
 // mark a buffer as written by the device
-inline void mark_device_written(uint32_t id) { g.bufs[id].shadow_valid = false; }
+void capture_const_dirty(void *dev);             // capture.cu: a step constant is overwritten inside the recorded step
+inline void mark_device_written(uint32_t id) { g.bufs[id].shadow_valid = false; if (g.bufs[id].step_const) capture_const_dirty(g.bufs[id].ptr); }
 // grid size helper: enough CTAs to fill the machine `waves` times over
 inline unsigned grid_for(uint64_t work_items, unsigned per_cta, unsigned max_ctas_per_sm = 16) {
     uint64_t need = (work_items + per_cta - 1) / per_cta;
@@ -115,6 +117,9 @@ uint32_t capture_first_id();                                    // first buffer 
 // give_back returns a block when the captured step frees the buffer
 void *capture_arena_alloc(uint64_t bytes);
 void capture_arena_give_back(void *ptr, uint64_t bytes);
+// A constant of the step being recorded (bytes the host wrote inside the step, the same at every replay): device memory
+// in the part of the step arena that is never handed out twice, filled now, outside the recording.  Null if there is no room.
+void *capture_const_place(const void *host, uint64_t host_bytes, uint64_t buf_bytes);
 bool capture_write_is_input(uint64_t bytes);                    // a host write of this size made inside a capture is per-step data, not a constant
 uint8_t *capture_arena_take(uint64_t bytes);                    // pinned host memory that lives as long as the graph
 int  capture_add_input(void *dst, const void *src, uint64_t bytes);
