@@ -220,7 +220,8 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
     the ranks and p <- p - lr/world * sum — runs as thvm_cuda_dp_sgd_step (`fused`), or as recorded: one all-reduce
     call over the gradient buffers and one dispatch + copy per parameter tensor.  Each step uploads its batch and
     one-hot labels from pinned host memory and reads the loss back; with the graph, the loss of step k is fetched while
-    step k + 1 runs, so the host never waits inside the timed loop except to stay one step behind the device."""
+    step k + 1 runs, and the batch of step k + 1 is uploaded on the copy stream while step k runs, so the host never waits inside
+    the timed loop except to stay one step behind the device."""
     import torch
     import torch.distributed as dist
     from tinyhvm_b200 import configs, replay, synth
@@ -284,8 +285,9 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
         # ---- timed loop: launches back to back, the loss of step k read while step k + 1 runs
         ring = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(4)]
         done = [torch.cuda.Event() for _ in range(4)]
-        for k in range(3):                                 # the loop body itself, untimed: first use of the read-back ring
-            graph.launch(ext(k))
+        for k in range(3):                                 # the loop body itself, untimed: first use of the read-back ring and of the staging slots
+            graph.prefetch(ext(k))
+            graph.launch_prefetched()
             graph.results_async({"loss": ring[k % 4].numpy()})
             done[k % 4].record(stream)
         done[2].synchronize()
@@ -294,10 +296,13 @@ def cnn_section(be, stream, rank: int, world: int, model: str = "lenet", steps: 
         be.sync(); torch.cuda.synchronize()
         launches0 = be.launches()
         t0 = time.perf_counter()
+        graph.prefetch(ext(4))
         for k in range(steps):
-            graph.launch(ext(4 + k))
+            graph.launch_prefetched()
             graph.results_async({"loss": ring[k % 4].numpy()})
             done[k % 4].record(stream)
+            if k + 1 < steps:
+                graph.prefetch(ext(5 + k))                 # the next batch travels on the copy stream while this step runs
             if k >= 1:                                     # stay one step behind the device
                 done[(k - 1) % 4].synchronize()
                 losses.append(float(ring[(k - 1) % 4][0]))

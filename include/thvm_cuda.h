@@ -279,6 +279,12 @@ int      thvm_cuda_capture_begin(void);
 int      thvm_cuda_capture_input(uint32_t id, const void *host, uint64_t bytes);
 int      thvm_cuda_capture_end(void);
 int      thvm_cuda_graph_set_input(int graph, int input, const void *host);
+/* Inputs travel host -> device staging -> buffer; the recorded node is the second hop.  graph_set_input uploads `host` on the
+ * backend's stream, after the launches already queued and before the next one (the bytes are read when the stream gets
+ * there: keep them unchanged until then).  graph_prefetch_input uploads the NEXT launch's bytes on the library's copy
+ * stream instead, into another of three staging slots, so the upload overlaps the step that is running; the next
+ * graph_launch waits for it and reads from that slot.  A launch with neither call replays the bytes of the one before. */
+int      thvm_cuda_graph_prefetch_input(int graph, int input, const void *host);
 int      thvm_cuda_graph_launch(int graph);
 int      thvm_cuda_graph_result(int graph, int result, void *out, uint64_t bytes);
 /* graph_result without the wait: the copy to `out` (pinned host memory) is queued behind the latest launch; `out` is

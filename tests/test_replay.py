@@ -266,8 +266,18 @@ def test_captured_step_graph_matches_recorded_run(tmp_path, cuda):
     nk, ncp, nms, no = (C.c_uint32() for _ in range(4))
     assert cuda.lib.thvm_cuda_graph_nodes(step.handle, C.byref(nk), C.byref(ncp), C.byref(nms), C.byref(no)) == 0
     assert nk.value == step.n_kernels and ncp.value >= 3 and no.value == 0, (nk.value, ncp.value, nms.value, no.value)
-    for s in range(2, steps):
-        step.launch(ext(s))
+    # steps 2 and 3: inputs uploaded on the main stream before the launch; steps 4 and 5: uploaded ahead on the copy
+    # stream while the step before them is still running, into another staging slot
+    keep = [ext(s) for s in range(steps)]                 # the host arrays stay alive until their step has run
+    for s in (2, 3):
+        step.launch(keep[s])
+        if s == 3:
+            step.prefetch(keep[4])
+        losses.append(float(step.results()["loss"][0]))
+    for s in (4, 5):
+        step.launch_prefetched()
+        if s == 4:
+            step.prefetch(keep[5])
         losses.append(float(step.results()["loss"][0]))
     for s in range(steps):
         assert abs(losses[s] - float(res[f"loss{s}"][0])) < 2e-5, s

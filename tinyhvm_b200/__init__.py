@@ -81,6 +81,7 @@ SYMBOLS = {
     "thvm_cuda_capture_input": (C.c_int, [_u32, _vp, _u64]),
     "thvm_cuda_capture_end": (C.c_int, []),
     "thvm_cuda_graph_set_input": (C.c_int, [C.c_int, C.c_int, _vp]),
+    "thvm_cuda_graph_prefetch_input": (C.c_int, [C.c_int, C.c_int, _vp]),
     "thvm_cuda_graph_launch": (C.c_int, [C.c_int]),
     "thvm_cuda_graph_result": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),
     "thvm_cuda_graph_result_async": (C.c_int, [C.c_int, C.c_int, _vp, _u64]),

@@ -8,10 +8,12 @@
 // usual (plan lookup, buffer ids, reference counts) but its stream work — kernels,
 // zero-fills, stream-ordered allocations and frees, copies, NCCL sums — is recorded
 // instead of run.  What differs from an eager step:
-//   * staged host->device writes take their pinned staging space from an arena the graph
-//     owns, so the bytes are still there at every launch (constants of the step);
-//   * data that changes from step to step is declared with capture_input: a copy node
-//     whose host source can be re-pointed before each launch (graph_set_input);
+//   * host->device writes that are not declared as inputs are constants of the step: placed
+//     once in a part of the step arena that is never recycled (or, without an arena, staged
+//     in pinned memory the graph owns and copied at every launch);
+//   * data that changes from step to step is declared with capture_input: it travels through
+//     device staging, uploaded before each launch (graph_set_input) or ahead of it on the
+//     copy stream while the previous step runs (graph_prefetch_input);
 //   * buf_read of device data records a copy into arena memory and hands back zeros;
 //     the values of a launch are fetched afterwards with graph_result;
 //   * nothing may wait for the stream, so the step must have run eagerly once before
@@ -29,7 +31,16 @@ struct Capture {
     cudaGraphExec_t exec = nullptr;
     std::vector<uint8_t *> chunks;                 // pinned arena, CHUNK bytes each (large requests get their own)
     uint64_t chunk_pos = 0, chunk_cap = 0;
-    struct Input { cudaGraphNode_t node; void *dst; uint64_t bytes; const void *src; uint8_t *stage; };
+    // A per-step input reaches its buffer through device staging: the recorded node is a device-to-device copy from one
+    // of three staging slots.  graph_set_input uploads into the slot the node reads, on the main stream, before the
+    // launch; graph_prefetch_input uploads the NEXT step's bytes into another slot on the copy stream while the current
+    // step runs, and the next launch re-points the node to it (three slots: the one being read by the running step, the
+    // one the queued step will read, the one being filled).
+    struct Input {
+        cudaGraphNode_t node; void *dst; uint64_t bytes;
+        uint8_t *stage[3]; cudaEvent_t filled[3], read[3]; bool read_valid[3];
+        int cur, pending;                          // slot the node reads now; slot a prefetch has filled for the next launch (-1: none)
+    };
     struct Result { uint8_t *host; uint64_t bytes; };
     std::vector<Input> inputs;
     std::vector<Result> results;
@@ -154,8 +165,13 @@ static cudaGraphNode_t last_captured_node() {
 // host -> device copy recorded as an input of the step
 int capture_add_input(void *dst, const void *src, uint64_t bytes) {
     Capture &c = *g.cap;
-    Capture::Input in{nullptr, dst, bytes, src, nullptr};
-    THC_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream));
+    Capture::Input in; memset(&in, 0, sizeof in);
+    in.dst = dst; in.bytes = bytes; in.cur = 0; in.pending = -1;
+    THC_CUDA_OK(cudaMalloc((void **)&in.stage[0], bytes));
+    // the bytes given now really travel (copy stream, not recording), so a launch without graph_set_input replays them
+    THC_CUDA_OK(cudaMemcpyAsync(in.stage[0], src, bytes, cudaMemcpyHostToDevice, g.copy_stream));
+    THC_CUDA_OK(cudaStreamSynchronize(g.copy_stream));     // the caller may free `src` when the call returns
+    THC_CUDA_OK(cudaMemcpyAsync(dst, in.stage[0], bytes, cudaMemcpyDeviceToDevice, g.stream));
     in.node = last_captured_node();
     if (!in.node) capture_fail("capture_input: the copy node could not be identified");
     c.inputs.push_back(in);
@@ -175,6 +191,12 @@ static void destroy(Capture *c) {
     if (c->exec) cudaGraphExecDestroy(c->exec);
     if (c->graph) cudaGraphDestroy(c->graph);
     for (uint8_t *p : c->chunks) cudaFreeHost(p);
+    for (Capture::Input &in : c->inputs)
+        for (int k = 0; k < 3; k++) {
+            if (in.stage[k]) cudaFree(in.stage[k]);
+            if (in.filled[k]) cudaEventDestroy(in.filled[k]);
+            if (in.read[k]) cudaEventDestroy(in.read[k]);
+        }
     if (c->arena) cudaFree(c->arena);
     delete c;
 }
@@ -284,10 +306,24 @@ int thvm_cuda_graph_set_input(int graph, int input, const void *host) {
     if (!c) return 1;
     if (input < 0 || (size_t)input >= c->inputs.size() || !host) { set_error("graph_set_input: input %d of %zu", input, c->inputs.size()); return 1; }
     Capture::Input &in = c->inputs[input];
-    if (in.src == host) return 0;
-    cudaError_t e = cudaGraphExecMemcpyNodeSetParams1D(c->exec, in.node, in.dst, host, in.bytes, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) { cudaGetLastError(); set_error("graph_set_input: %s", cudaGetErrorString(e)); return 1; }
-    in.src = host;
+    // stream order puts this upload after every earlier launch (which read the slot) and before the next one
+    THC_CUDA_OK(cudaMemcpyAsync(in.stage[in.cur], host, in.bytes, cudaMemcpyHostToDevice, g.stream));
+    in.pending = -1;
+    return 0;
+}
+
+int thvm_cuda_graph_prefetch_input(int graph, int input, const void *host) {
+    Capture *c = graph_of(graph, "graph_prefetch_input");
+    if (!c) return 1;
+    if (input < 0 || (size_t)input >= c->inputs.size() || !host) { set_error("graph_prefetch_input: input %d of %zu", input, c->inputs.size()); return 1; }
+    Capture::Input &in = c->inputs[input];
+    const int slot = in.pending >= 0 ? in.pending : (in.cur + 1) % 3;
+    if (!in.stage[slot]) THC_CUDA_OK(cudaMalloc((void **)&in.stage[slot], in.bytes));
+    if (!in.filled[slot]) THC_CUDA_OK(cudaEventCreateWithFlags(&in.filled[slot], cudaEventDisableTiming));
+    if (in.read_valid[slot]) THC_CUDA_OK(cudaStreamWaitEvent(g.copy_stream, in.read[slot], 0));    // the launch that last read this slot is done
+    THC_CUDA_OK(cudaMemcpyAsync(in.stage[slot], host, in.bytes, cudaMemcpyHostToDevice, g.copy_stream));
+    THC_CUDA_OK(cudaEventRecord(in.filled[slot], g.copy_stream));
+    in.pending = slot;
     return 0;
 }
 
@@ -295,8 +331,20 @@ int thvm_cuda_graph_launch(int graph) {
     Capture *c = graph_of(graph, "graph_launch");
     if (!c) return 1;
     if (g.cap) { set_error("graph_launch: a capture is running"); return 1; }
+    for (Capture::Input &in : c->inputs) {
+        if (in.pending < 0) continue;
+        cudaError_t e = cudaGraphExecMemcpyNodeSetParams1D(c->exec, in.node, in.dst, in.stage[in.pending], in.bytes, cudaMemcpyDeviceToDevice);
+        if (e != cudaSuccess) { cudaGetLastError(); set_error("graph_launch: re-pointing an input: %s", cudaGetErrorString(e)); return 1; }
+        THC_CUDA_OK(cudaStreamWaitEvent(g.stream, in.filled[in.pending], 0));
+        in.cur = in.pending; in.pending = -1;
+    }
     cudaError_t e = cudaGraphLaunch(c->exec, g.stream);
     if (e != cudaSuccess) { cudaGetLastError(); set_error("graph_launch: %s", cudaGetErrorString(e)); return 1; }
+    for (Capture::Input &in : c->inputs) {
+        if (!in.read[in.cur]) THC_CUDA_OK(cudaEventCreateWithFlags(&in.read[in.cur], cudaEventDisableTiming));
+        THC_CUDA_OK(cudaEventRecord(in.read[in.cur], g.stream));
+        in.read_valid[in.cur] = true;
+    }
     g.launches += c->launches;
     return 0;
 }

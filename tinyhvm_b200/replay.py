@@ -198,6 +198,21 @@ class CapturedStep:
             assert self.lib.thvm_cuda_graph_set_input(self.handle, idx, src.ctypes.data) == 0, self.be.last_error()
         assert self.lib.thvm_cuda_graph_launch(self.handle) == 0, self.be.last_error()
 
+    def prefetch(self, externals: dict) -> None:
+        """Upload the NEXT launch's inputs now, on the library's copy stream, while the step just launched runs; follow
+        with `launch_prefetched()`.  The arrays must stay alive and unchanged until that launch has started."""
+        self._next = []
+        for idx, (name, k, nb) in enumerate(self.inputs):
+            src = externals[name]
+            src = src[k % len(src)] if isinstance(src, (list, tuple)) else src
+            assert src.nbytes == nb
+            self._next.append(src)
+            assert self.lib.thvm_cuda_graph_prefetch_input(self.handle, idx, src.ctypes.data) == 0, self.be.last_error()
+
+    def launch_prefetched(self) -> None:
+        self._alive = self._next
+        assert self.lib.thvm_cuda_graph_launch(self.handle) == 0, self.be.last_error()
+
     def results_async(self, outs: dict) -> None:
         """Queue copies of the named results of the latest launch into the caller's pinned arrays (`outs[name]`);
         they are valid once the stream has passed this point."""
