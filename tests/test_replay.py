@@ -370,3 +370,62 @@ def test_refused_capture_leaves_older_buffers_as_they_were(cuda):
     assert np.array_equal(cuda.read(out2, np.float32, n), x + np.float32(2.5))
     cuda.reset(0)
     assert cuda.last_error() == ""
+
+
+@pytest.mark.gpu
+def test_step_constants_are_uploaded_once_and_survive_a_step_that_overwrites_them(cuda):
+    """What the host writes inside a recorded step is a constant of the step: it gets no copy node (it is placed in the
+    never-recycled part of the step arena and uploaded while the step is recorded).  A step that overwrites such a
+    constant with a kernel still sees the original bytes at every replay, because a put-back copy ends the graph."""
+    from tinyhvm_b200 import abi
+    from tinyhvm_b200.abi import ADD, Dispatch, Leaf
+    cuda.reset(0)
+    n = 4096
+    v = abi.view_contiguous([n])
+    table = np.linspace(-1, 1, n).astype(np.float32)
+    add_scalar = Dispatch([Leaf(table, v), Leaf(np.array([2.5], np.float32), abi.view_contiguous([1]))], [(ADD, 0, 1)], [n])
+    add_table = Dispatch([Leaf(table, v), Leaf(table, v)], [(ADD, 0, 1)], [n])
+    add_s = Dispatch([Leaf(np.zeros(1, np.float32), abi.view_contiguous([1])), Leaf(np.zeros(1, np.float32), abi.view_contiguous([1]))], [(ADD, 0, 1)], [1])
+    bx, out = cuda.alloc(n * 4), cuda.alloc(n * 4)              # older than the step: the input and the result
+    keep = out
+
+    def step(overwrite: bool):
+        cs = cuda.upload(np.array([2.5], np.float32))           # 4 bytes: host shadow until a kernel needs it
+        cl = cuda.upload(table)                                 # 16 KB: device memory at once, then the host write
+        t = cuda.alloc(n * 4)
+        cuda.dispatch_ids(t, [bx, cs], add_scalar)              # t = x + 2.5
+        cuda.dispatch_ids(out, [t, cl], add_table)              # out = t + table
+        if overwrite:
+            cuda.dispatch_ids(cl, [cl, cs], add_scalar)         # the step clobbers both constants afterwards
+            cuda.dispatch_ids(cs, [cs, cs], add_s)
+        res = cuda.read(out, np.float32, n)
+        cuda.reset(keep)
+        return res
+
+    for overwrite in (False, True):
+        x0 = np.arange(n, dtype=np.float32)
+        cuda.write(bx, x0)
+        assert np.array_equal(step(overwrite), x0 + np.float32(2.5) + table)      # eager: plans built
+        cuda.sync()
+        cuda.reset(keep)
+        step(overwrite)                                                          # a finished step sizes the arena
+        assert cuda.lib.thvm_cuda_capture_begin() == 0
+        xin = np.ascontiguousarray(x0)
+        assert cuda.lib.thvm_cuda_capture_input(bx, xin.ctypes.data, xin.nbytes) == 0
+        step(overwrite)
+        gr = cuda.lib.thvm_cuda_capture_end()
+        assert gr > 0, cuda.last_error()
+        nk, ncp, nms, no = (C.c_uint32() for _ in range(4))
+        assert cuda.lib.thvm_cuda_graph_nodes(gr, C.byref(nk), C.byref(ncp), C.byref(nms), C.byref(no)) == 0
+        # copies: the input's second hop and the result read-back; plus one put-back per clobbered constant
+        assert ncp.value == (4 if overwrite else 2), (overwrite, nk.value, ncp.value, nms.value, no.value)
+        for k in range(3):
+            xk = (x0 * (k + 1)).astype(np.float32)
+            assert cuda.lib.thvm_cuda_graph_set_input(gr, 0, xk.ctypes.data) == 0
+            assert cuda.lib.thvm_cuda_graph_launch(gr) == 0
+            got = np.empty(n, np.float32)
+            assert cuda.lib.thvm_cuda_graph_result(gr, 0, got.ctypes.data, got.nbytes) == 0
+            assert np.array_equal(got, xk + np.float32(2.5) + table), (overwrite, k)
+        cuda.lib.thvm_cuda_graph_destroy(gr)
+    cuda.reset(0)
+    assert cuda.last_error() == ""
