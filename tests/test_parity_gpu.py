@@ -229,10 +229,11 @@ def contraction_cases():
         # convolutions whose re-laid operands arrive by tile loads: 32 and 64 input channels, output widths 16 and 32
         cases.conv_fprop_case(rng, 2, 32, 18, 18, 64, 3), cases.conv_fprop_case(rng, 1, 64, 34, 34, 32, 3),
         cases.conv_fprop_case(rng, 4, 192, 10, 10, 32, 3), cases.conv_fprop_case(rng, 3, 32, 13, 21, 48, 3),   # long K (split), odd sizes
+        cases.conv_fprop_case(rng, 2, 32, 18, 18, 256, 3), cases.conv_fprop_case(rng, 2, 64, 18, 18, 200, 3),  # two column tiles on the persistent kernel, the second ragged
         # weight gradients by tile loads over shifted copies: 32, 64 and 256 input channels (4, 2 and half a tap per CTA)
         cases.conv_wgrad_case(rng, 4, 32, 18, 18, 64, 3), cases.conv_wgrad_case(rng, 1, 64, 34, 34, 32, 3),
         cases.conv_wgrad_case(rng, 2, 256, 18, 18, 32, 3),
-        cases.conv_wgrad_case(rng, 2, 32, 66, 66, 64, 3),          # output rows of 64: the gradient is read in place, two k-blocks per row
+        cases.conv_wgrad_case(rng, 1, 32, 34, 66, 64, 3),          # output rows of 64: the gradient is read in place, two k-blocks per row
         # thin shapes on the CUDA-core kernels: many rows x few columns, and few outputs x very long K
         cases.conv_fprop_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 5000, 40, 12), cases.mm_case(rng, 4100, 290, 27),
         cases.conv_wgrad_case(rng, 32, 1, 32, 32, 6, 5), cases.mm_case(rng, 10, 6000, 20), cases.mm_case(rng, 16, 9000, 150, ta=True),
