@@ -162,6 +162,15 @@ def pad_case(rng, B, Cc, H, W, p):
     return Dispatch([x, scalar_leaf(0.0, 4)], [(ADD, 0, 1)], full, name=f"pad_b{B}c{Cc}h{H}w{W}p{p}")
 
 
+def crop_case(rng, B, Cc, H, W, p, q=None):
+    """ADD(shrink(x), 0): the H x W window at (p, q) of every (H + 2p) x (W + 2q) plane, as a convolution's input
+    gradient is cut out of its padded form."""
+    q = p if q is None else q
+    x = dense(rng, [B, Cc, H + 2 * p, W + 2 * q])
+    x.view = abi.view_shrink(x.view, [0, 0, p, q], [B, Cc, p + H, q + W])
+    return Dispatch([x, scalar_leaf(0.0, 4)], [(ADD, 0, 1)], [B, Cc, H, W], name=f"crop_b{B}c{Cc}h{H}w{W}p{p}q{q}")
+
+
 def bias_grad_case(rng, M, N):
     return Dispatch([dense(rng, [M, N])], [], [M, N], [0], SUM, name=f"bias_grad_{M}x{N}")
 

@@ -292,15 +292,18 @@ def test_read_back_variants(cuda):
 
 def test_layout_copy_kernels(cuda, oracle):
     """Padding materialised as ADD(pad(x), 0) (src/tensor/view/pad.c:2-16: a mask and a negative offset, never a copy)
-    and the pool gradient's window-to-plane permute run on their own bandwidth kernels when the planes are contiguous;
+    the opposite cut (SHRINK materialised) and the pool gradient's window-to-plane permute run on their own bandwidth
+    kernels when the planes are contiguous;
     shapes those kernels decline (odd extents, permuted planes) fall to the general forms.  Bit for bit either way."""
     rng = np.random.default_rng(31)
     eligible = [(cases.pad_case(rng, 3, 5, 16, 16, 1), "pad_planes"), (cases.pad_case(rng, 2, 1, 28, 28, 2), "pad_planes"),
                 (cases.pad_case(rng, 4, 64, 64, 64, 1), "pad_planes"), (cases.pad_case(rng, 1, 7, 9, 30, 1), "pad_planes"),
                 (cases.permute_copy_case(rng, [2, 3, 4, 6, 2, 2], [0, 1, 2, 4, 3, 5]), "window_to_plane"),
                 (cases.permute_copy_case(rng, [4, 64, 32, 32, 2, 2], [0, 1, 2, 4, 3, 5]), "window_to_plane"),
-                (cases.permute_copy_case(rng, [5, 8, 2, 2], [0, 2, 1, 3]), "window_to_plane")]
-    declined = [cases.pad_case(rng, 2, 3, 5, 7, 2), cases.permute_copy_case(rng, [2, 3, 4, 5, 2, 2], [0, 1, 2, 4, 3, 5]),
+                (cases.permute_copy_case(rng, [5, 8, 2, 2], [0, 2, 1, 3]), "window_to_plane"),
+                (cases.crop_case(rng, 3, 5, 16, 16, 1), "crop_planes"), (cases.crop_case(rng, 2, 64, 64, 64, 1), "crop_planes"),
+                (cases.crop_case(rng, 2, 1, 28, 28, 2), "crop_planes"), (cases.crop_case(rng, 1, 7, 9, 32, 2, 1), "crop_planes")]
+    declined = [cases.pad_case(rng, 2, 3, 5, 7, 2), cases.crop_case(rng, 2, 3, 5, 7, 2), cases.permute_copy_case(rng, [2, 3, 4, 5, 2, 2], [0, 1, 2, 4, 3, 5]),
                 cases.permute_copy_case(rng, [2, 3, 4, 6, 2, 2], [1, 0, 2, 4, 3, 5])]
     for d, plan in eligible:
         got = cuda.run(d)
@@ -308,6 +311,6 @@ def test_layout_copy_kernels(cuda, oracle):
         assert same(got, oracle.run(d)), d.name
     for d in declined:
         got = cuda.run(d)
-        assert cuda.last_plan() not in ("pad_planes", "window_to_plane"), (d.name, cuda.last_plan())
+        assert cuda.last_plan() not in ("pad_planes", "window_to_plane", "crop_planes"), (d.name, cuda.last_plan())
         assert same(got, oracle.run(d)), d.name
     assert cuda.last_error() == ""

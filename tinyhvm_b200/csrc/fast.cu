@@ -731,7 +731,7 @@ static bool build_fast(const GenDesc &H, FastDesc &F) {
 
 void classify_plan(Plan *p) {
     if (try_contraction(p)) return;
-    if (try_pool2x2(p) || try_pool2x2_bwd(p) || try_pad2d(p) || try_window_to_plane(p)) return;
+    if (try_pool2x2(p) || try_pool2x2_bwd(p) || try_pad2d(p) || try_window_to_plane(p) || try_crop2d(p)) return;
     FastDesc *F = new FastDesc();
     if (build_fast(p->host, *F)) { p->fast = (struct FastDesc *)F; p->kind = F->strategy == 0 ? PLAN_EW : PLAN_REDUCE; }
     else { delete F; p->fast = nullptr; p->kind = PLAN_GENERIC; }
@@ -802,6 +802,7 @@ bool launch_fast(Plan *p, const GenArgs &args) {
     if (p->kind == PLAN_POOL_BWD) return launch_pool2x2_bwd(p, args);
     if (p->kind == PLAN_PAD2D) return launch_pad2d(p, args);
     if (p->kind == PLAN_WIN2PLANE) return launch_window_to_plane(p, args);
+    if (p->kind == PLAN_CROP2D) return launch_crop2d(p, args);
     FastDesc &F = *(FastDesc *)p->fast;
     FDesc D = F.d;
     for (unsigned i = 0; i < D.prog.n_leaves; i++) {

@@ -1,7 +1,8 @@
-// layout.cu — bandwidth kernels for the two layout-changing copies every convolutional training step is full of:
+// layout.cu — bandwidth kernels for the layout-changing copies every convolutional training step is full of:
 //   * padding materialised as ADD(pad(x), z): out[.., y, x] = in[.., y - pt, x - pl] + z inside the mask, 0 + z outside
 //     (src/tensor/view/pad.c:2-16 turns PAD into a mask and a negative offset; the staged convolutions realise it
 //     before the convolution reads it);
+//   * the opposite, a window cut out of every padded plane (SHRINK materialised): the valid part of a gradient;
 //   * window layout back to plane layout, out[.., oy, i, ox, j] = in[.., oy, ox, i, j] + z: the copy that follows the
 //     max-pool gradient (the pooled dims are split into windows by reshape + permute, src/nn/conv.c:484-513).
 // The general elementwise kernel decodes a rank-4..6 coordinate per pair of outputs for these (innermost dims of 66
@@ -33,6 +34,27 @@ __global__ void __launch_bounds__(256) k_pad2d(const float *__restrict__ x, cons
             v[i] = has_z ? __fadd_rn(in, z) : in;
             if (++xx == Wp) { xx = 0; yy++; }
         }
+        dst[q] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// The opposite copy: an H x W window cut out of every plane of pitch Ws (a SHRINK, e.g. the valid part of a padded
+// gradient), out[plane, y, x] = in[plane * Ps + (y * Ws + x)] + z with `in` already at the window's first element.
+// grid.x = plane, grid.y * 256 threads cover the plane's H * W / 4 groups of four outputs (W is a multiple of 4, so a
+// group never leaves its row); the source rows start anywhere, so they are read element by element, 128 bytes per warp.
+__global__ void __launch_bounds__(256) k_crop2d(const float *__restrict__ x, const float *__restrict__ zp, float *__restrict__ y,
+                                                unsigned H, unsigned W, unsigned Ws, unsigned long long Ps, unsigned has_z) {
+    const unsigned long long plane = blockIdx.x;
+    const unsigned quads = H * W / 4u;
+    const float z = has_z ? zp[0] : 0.0f;
+    const float *src = x + plane * Ps;
+    float4 *dst = reinterpret_cast<float4 *>(y + plane * (unsigned long long)H * W);
+    for (unsigned q = blockIdx.y * 256u + threadIdx.x; q < quads; q += gridDim.y * 256u) {
+        const unsigned f = 4u * q, yy = f / W, xx = f - yy * W;
+        const float *s = src + (unsigned long long)yy * Ws + xx;
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float in = __ldg(s + i); v[i] = has_z ? __fadd_rn(in, z) : in; }
         dst[q] = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
@@ -118,6 +140,55 @@ bool launch_pad2d(Plan *p, const GenArgs &args) {
     profile_begin();
     k_pad2d<<<dim3((unsigned)p->pool_planes, gy), 256, 0, g.stream>>>((const float *)args.leaf[src], z, (float *)args.out, p->pool_h, p->pool_w, Hp, Wp, pt, pl, sc >= 0 ? 1u : 0u);
     after_launch("pad_planes");
+    return true;
+}
+
+bool try_crop2d(Plan *p) {
+    const GenDesc &H = p->host;
+    int src, sc;
+    if (!copy_or_add_scalar(H, src, sc)) return false;
+    const DLeaf &L = H.leaves[src];
+    const int r = (int)H.rank;
+    if (r < 3 || (int)L.v.rank != r || L.v.has_mask || L.v.n_cm || L.v.offset < 0) return false;
+    for (int d = 0; d < r; d++) if (L.v.dims[d] != H.full_dims[d]) return false;
+    const unsigned Hc = H.full_dims[r - 2], Wc = H.full_dims[r - 1];
+    if (L.v.strides[r - 1] != 1 || L.v.strides[r - 2] <= (int)Wc || Wc % 4 != 0 || Hc == 0) return false;     // (pitch == W is a plain copy: other kernels)
+    const unsigned Ws = (unsigned)L.v.strides[r - 2];
+    // the planes form one run of constant pitch Ps
+    int d0 = r - 3;
+    while (d0 >= 0 && H.full_dims[d0] == 1) d0--;
+    if (d0 < 0) return false;
+    const long long Ps = L.v.strides[d0];
+    if (Ps < (long long)(Hc - 1) * Ws + Wc) return false;
+    unsigned long long planes = 1, want = (unsigned long long)Ps;
+    for (int d = r - 3; d >= 0; d--) {
+        if (H.full_dims[d] != 1 && (unsigned long long)L.v.strides[d] != want) return false;
+        planes *= H.full_dims[d]; want *= H.full_dims[d];
+    }
+    if (planes > 0x7FFFFFFFull || (unsigned long long)Hc * Wc > 0xFFFFFFFFull) return false;
+    p->pool_planes = planes; p->pool_h = Hc; p->pool_w = Wc;
+    p->pool_off = L.v.offset;                       // first element of the window in plane 0
+    p->pool_g_off = (Ps << 32) | (long long)Ws;     // plane pitch / row pitch (both below 2^31: strides are 32-bit)
+    p->pool_m_off = src; p->pool_one_off = sc >= 0 ? H.leaves[sc].v.offset : 0;
+    p->kind = PLAN_CROP2D;
+    return true;
+}
+
+bool launch_crop2d(Plan *p, const GenArgs &args) {
+    const int src = (int)p->pool_m_off, sc = p->host.n_leaves == 2 ? 1 - src : -1;
+    const unsigned long long Ps = (unsigned long long)(p->pool_g_off >> 32);
+    const unsigned Ws = (unsigned)(p->pool_g_off & 0xFFFFFFFFll);
+    const unsigned long long last = (unsigned long long)p->pool_off + (p->pool_planes - 1) * Ps + (unsigned long long)(p->pool_h - 1) * Ws + p->pool_w - 1;
+    if (last >= args.cap[src] || (sc >= 0 && (unsigned long long)p->pool_one_off >= args.cap[sc])) return false;   // the checked generic kernel runs instead
+    if (reinterpret_cast<uintptr_t>(args.out) & 15u) return false;
+    const float *z = sc >= 0 ? (const float *)args.leaf[sc] + p->pool_one_off : nullptr;
+    const unsigned quads = p->pool_h * p->pool_w / 4u;
+    unsigned gy = (quads + 255u) / 256u;
+    if (gy > 8u) gy = 8u;
+    if (g.profile_level >= 2) snprintf(g.last_shape, sizeof g.last_shape, "planes=%llu %ux%u out of pitch %u", p->pool_planes, p->pool_h, p->pool_w, Ws);
+    profile_begin();
+    k_crop2d<<<dim3((unsigned)p->pool_planes, gy), 256, 0, g.stream>>>((const float *)args.leaf[src] + p->pool_off, z, (float *)args.out, p->pool_h, p->pool_w, Ws, Ps, sc >= 0 ? 1u : 0u);
+    after_launch("crop_planes");
     return true;
 }
 

@@ -14,6 +14,7 @@ enum PlanKind : int {
     PLAN_POOL_BWD,      // the mask-form gradient of that pool -> pooling backward kernel (uop.cu)
     PLAN_PAD2D,         // padding of contiguous planes materialised (layout.cu)
     PLAN_WIN2PLANE,     // 2x2-window layout copied back to plane layout (layout.cu)
+    PLAN_CROP2D,        // a window cut out of every plane of a larger pitch (layout.cu)
 };
 
 struct FastDesc;        // family-specific, defined in fast_desc.h
@@ -52,6 +53,8 @@ bool launch_pool2x2_bwd(Plan *p, const GenArgs &args);
 // layout-changing copies (layout.cu)
 bool try_pad2d(Plan *p);
 bool launch_pad2d(Plan *p, const GenArgs &args);
+bool try_crop2d(Plan *p);
+bool launch_crop2d(Plan *p, const GenArgs &args);
 bool try_window_to_plane(Plan *p);
 bool launch_window_to_plane(Plan *p, const GenArgs &args);
 
